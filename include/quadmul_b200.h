@@ -1,0 +1,153 @@
+/*
+ * quadmul_b200 -- C ABI of the B200 (sm_100a) packed signed-int4 GEMM.
+ *
+ *   C[M,N] (int32, row-major) = A[M,K] (s4) * B[N,K]^T (s4)
+ *
+ * Operand layout (identical to carsonpo/quadmul, so the library is a drop-in for its
+ * GEMM path): two two's-complement nibbles per byte, element 2j in the LOW nibble and element
+ * 2j+1 in the HIGH nibble of byte j (reference: test.py:14, kernel.cu:395-396, kernel.cu:387);
+ * A is row-major M x K/2 bytes, B is N x K/2 bytes (K contiguous: "B is transposed",
+ * reference kernel.cu:77-78); C is M x N int32 and is fully overwritten.
+ *
+ * All pointers are DEVICE pointers on the current CUDA device unless a function says "host".
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Calls are
+ * asynchronous on that stream; nothing here synchronises unless stated.  Every function returns
+ * a qm_status_t and never fails silently; there is no CPU fallback.
+ */
+#ifndef QUADMUL_B200_H
+#define QUADMUL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum qm_status {
+    QM_OK = 0,
+    QM_ERR_NULL = 1,      /* a required pointer is NULL                                   */
+    QM_ERR_SHAPE = 2,     /* m, n, k not positive, k odd, or sizes overflow the kernel     */
+    QM_ERR_ALIGN = 3,     /* reserved: operands the selected kernel cannot address         */
+    QM_ERR_CUDA = 4,      /* a CUDA runtime/driver call failed (see qm_last_cuda_error)    */
+    QM_ERR_TIMEOUT = 5,   /* a bounded in-kernel wait expired (see qm_device_status)       */
+    QM_ERR_ARCH = 6,      /* the current device is not compute capability 10.x             */
+    QM_ERR_WORKSPACE = 7, /* caller-provided or built-in scratch is too small              */
+    QM_ERR_ARG = 8        /* an option value is out of range                               */
+} qm_status_t;
+
+/* Kernel families the dispatcher chooses from.  QM_KERNEL_AUTO lets the tile table decide. */
+typedef enum qm_kernel {
+    QM_KERNEL_AUTO = 0,
+    QM_KERNEL_TC = 1,  /* TMA + mbarrier ring + in-smem s4->s8 + tcgen05.mma kind::i8 + TMEM   */
+    QM_KERNEL_SIMT = 2 /* dp4a kernel for shapes/alignments the tensor path does not take      */
+} qm_kernel_t;
+
+/* Options for qm_gemm_s4_ex.  Zero-initialise for defaults. */
+typedef struct qm_gemm_opts {
+    int kernel;     /* qm_kernel_t                                                              */
+    int tile_n;     /* 0 = table; UMMA N extent of the CTA tile: 16..256 (multiple of 16)       */
+    int swap_ab;    /* 0 = table, 1 = C rows on UMMA-M (prefill form), 2 = C columns on UMMA-M  */
+    int split_k;    /* 0 = table; >= 1 number of K partitions reduced through scratch memory    */
+    int cta_pair;   /* 0 = table, 1 = single-CTA MMA, 2 = two-CTA (cta_group::2) MMA            */
+    int reserved[3];
+} qm_gemm_opts_t;
+
+const char *qm_status_string(int status);
+int qm_version(void);
+
+/* Text of the last CUDA error this thread saw inside the library ("" if none). */
+const char *qm_last_cuda_error(void);
+
+/*
+ * One-time per-device set-up (status word, split-K scratch, kernel attributes).  Optional: the
+ * first qm_gemm_s4 on a device does it implicitly, but that first call then allocates, so call
+ * qm_init before capturing a CUDA graph.  Replaces nothing in the reference (it has no set-up;
+ * reference kernel.cu:268-289 launches unconditionally).
+ */
+int qm_init(int device);
+
+/*
+ * The GEMM.  Replaces `wrapper(void*A, void*B, void*C, int m, int n, int k, cudaStream_t)`
+ * (reference kernel.cu:334-385) behind `quadmul.gemm` (reference extension.cpp:8-24).  Unlike the
+ * reference, every (m, n, k) with k even is accepted; shapes the tensor path cannot take
+ * (k % 32 != 0, pointers not 16-byte aligned, k >= 131072) run on the dp4a kernel instead.
+ */
+int qm_gemm_s4(const void *A, const void *B, void *C, int m, int n, int k, void *stream);
+
+/* Same, with explicit kernel/tile choices (used by the tuner and the tests). */
+int qm_gemm_s4_ex(const void *A, const void *B, void *C, int m, int n, int k, void *stream,
+                  const qm_gemm_opts_t *opts);
+
+/*
+ * Same product with a leading dimension for C (elements): writes C[r * ldc + c].  Lets a rank that
+ * owns a block of B's rows write its column slab straight into a full-width C.
+ */
+int qm_gemm_s4_ldc(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc,
+                   void *stream);
+
+/*
+ * HOST-buffer form for FFI callers that hold plain memory: copies A and B to the device, runs
+ * the GEMM, copies C back and synchronises.  hA: m*k/2 bytes, hB: n*k/2 bytes, hC: m*n int32.
+ * Replaces the sequence cudaMalloc/cudaMemcpy/launch/cudaMemcpy of the reference's stand-alone
+ * harness (reference kernel.cu:457-508).
+ */
+int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int k);
+
+/*
+ * Pack int8 values in [-8, 7] (rows x k, k even) into nibbles (rows x k/2 bytes).
+ * Replaces the Python `pack_b` (reference test.py:6-15).
+ */
+int qm_pack_s4(const void *in_s8, void *out_packed, int64_t rows, int64_t k, void *stream);
+
+/*
+ * Unpack nibbles (rows x k/2 bytes) into sign-extended int8 (rows x k).
+ * Replaces the host function `unpack_int4_matrix` (reference kernel.cu:389-408).
+ */
+int qm_unpack_s4(const void *in_packed, void *out_s8, int64_t rows, int64_t k, void *stream);
+
+/*
+ * Fill a packed matrix with the counter-based generator value(seed,row,col) in [-8, 7]
+ * (splitmix64 of seed + row*k + col, bits 33..36, minus 8).  Stands in for
+ * `torch.randint` + `pack_b` of the reference's test (reference test.py:22-27).
+ */
+int qm_fill_s4(void *out_packed, int64_t rows, int64_t k, uint64_t seed, void *stream);
+
+/*
+ * Column-sharded multi-GPU helpers.  Rank `rank` of `world` owns B rows
+ * [*begin, *begin + *count), i.e. the columns of C with those indices.  The split is contiguous,
+ * in units of 128 columns where n allows, remainder to the last ranks.  No counterpart in the
+ * reference (it is single-GPU).
+ */
+int qm_nshard_range(int n, int world, int rank, int *begin, int *count);
+
+/*
+ * Rank-major gathered slabs [world][m][*] (as an all-gather of per-rank column slabs produces,
+ * each rank's slab padded to `slab_stride` elements) -> row-major C[m][n].
+ */
+int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t slab_stride,
+                 void *stream);
+
+/*
+ * In-kernel wait status of the current device: *code is 0 or QM_ERR_TIMEOUT, *where identifies
+ * the wait that gave up.  Synchronises the device.  `clear` != 0 resets the word.
+ */
+int qm_device_status(int *code, int *where, int clear);
+
+/* What the dispatcher would run for (m, n, k): fills *opts with the resolved choices. */
+int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts);
+
+#ifdef __cplusplus
+}
+#endif
+
+#ifdef __cplusplus
+/*
+ * The reference's C++ entry point, kept with its exact signature and linkage (reference
+ * extension.cpp:6, kernel.cu:334) so code that declares it links unchanged.  Errors, which the
+ * reference drops, are reported on stderr once per distinct status.
+ */
+struct CUstream_st;
+void wrapper(void *A, void *B, void *C, const int m, const int n, const int k, CUstream_st *stream);
+#endif
+
+#endif /* QUADMUL_B200_H */

@@ -1,0 +1,69 @@
+"""In-tree build of the CUDA library: nvcc, sm_100a only, no torch involved.
+
+    python -m quadmul_b200.build [--force] [--verbose]
+
+Produces quadmul_b200/libquadmul_b200.so (the C ABI declared in include/quadmul_b200.h).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_PATH = os.path.join(PKG_DIR, "libquadmul_b200.so")
+SOURCES = ["qm_api.cu", "qm_gemm_tc.cu", "qm_gemm_simt.cu", "qm_pack.cu"]
+HEADERS = ["qm_internal.h", "qm_ptx.cuh", "qm_tile_table.h", os.path.join("..", "..", "include", "quadmul_b200.h")]
+
+
+def nvcc_path() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; set NVCC or install the CUDA toolkit")
+    return cand
+
+
+def sources() -> list[str]:
+    return [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = sources() + [os.path.join(CSRC, h) for h in HEADERS]
+    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not is_stale():
+        return LIB_PATH
+    cmd = [
+        nvcc_path(),
+        "-std=c++17",
+        "-O3",
+        "-gencode",
+        "arch=compute_100a,code=sm_100a",
+        "-lineinfo",
+        "--expt-relaxed-constexpr",
+        "-Xcompiler",
+        "-fPIC,-O3,-Wall",
+        "-shared",
+        "-o",
+        LIB_PATH,
+    ]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += sources()
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libquadmul_b200.so")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,311 @@
+// C ABI of the library (include/quadmul_b200.h): argument checks, per-device set-up, dispatch.
+// This layer stands where the reference has `wrapper` (kernel.cu:334-385) and the pybind
+// function `gemm` (extension.cpp:8-24).
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "qm_internal.h"
+#include "qm_tile_table.h"
+
+namespace qm {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_mutex;
+thread_local std::string t_last_error;
+
+struct HostStage {  // grow-only device buffers of qm_gemm_s4_host
+    void *a = nullptr, *b = nullptr, *c = nullptr;
+    size_t a_bytes = 0, b_bytes = 0, c_bytes = 0;
+};
+HostStage g_stage[kMaxDevices];
+
+int ensure_ctx(DeviceCtx **out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return QM_ERR_ARG;
+    DeviceCtx &c = g_ctx[dev];
+    if (!c.ready) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!c.ready) {
+            int major = 0, sms = 0;
+            if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+                return record_cuda_error(e, "cudaDeviceGetAttribute");
+            if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+                return record_cuda_error(e, "cudaDeviceGetAttribute");
+            if (major != 10) return QM_ERR_ARCH;
+            int *status = nullptr;
+            if ((e = cudaMalloc(&status, 2 * sizeof(int))) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(status)");
+            if ((e = cudaMemset(status, 0, 2 * sizeof(int))) != cudaSuccess) return record_cuda_error(e, "cudaMemset(status)");
+            int st = tc_prepare_device();
+            if (st != QM_OK) {
+                cudaFree(status);
+                return st;
+            }
+            c.device = dev;
+            c.cc_major = major;
+            c.num_sms = sms;
+            c.status = status;
+            c.ready = true;
+        }
+    }
+    *out = &c;
+    return QM_OK;
+}
+
+int check_gemm_args(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc)
+{
+    if (m < 0 || n < 0 || k < 0 || (k & 1)) return QM_ERR_SHAPE;
+    if (m == 0 || n == 0) return QM_OK;
+    if (!C) return QM_ERR_NULL;
+    if (ldc < n) return QM_ERR_SHAPE;
+    if (k > 0 && (!A || !B)) return QM_ERR_NULL;
+    return QM_OK;
+}
+
+int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc, void *stream,
+                  const qm_gemm_opts_t *opts)
+{
+    int st = check_gemm_args(A, B, C, m, n, k, ldc);
+    if (st != QM_OK) return st;
+    if (m == 0 || n == 0) return QM_OK;
+    DeviceCtx *ctx = nullptr;
+    st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), static_cast<int32_t *>(C), m, n, k, ldc,
+               static_cast<cudaStream_t>(stream)};
+    if (k == 0) {  // empty sum: C = 0
+        cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)n * 4, (size_t)m, g.stream);
+        return e == cudaSuccess ? QM_OK : record_cuda_error(e, "cudaMemset2DAsync");
+    }
+    int kernel = opts ? opts->kernel : QM_KERNEL_AUTO;
+    if (kernel < QM_KERNEL_AUTO || kernel > QM_KERNEL_SIMT) return QM_ERR_ARG;
+    const bool eligible = tc_eligible(g);
+    if (kernel == QM_KERNEL_TC && !eligible) return QM_ERR_ALIGN;
+    if (kernel == QM_KERNEL_AUTO) kernel = eligible ? QM_KERNEL_TC : QM_KERNEL_SIMT;
+    if (kernel == QM_KERNEL_SIMT) return simt_launch(g);
+
+    TcPlan p = plan_tc(m, n, k, ctx->num_sms);
+    if (opts) {
+        if (opts->swap_ab < 0 || opts->swap_ab > 2 || opts->split_k < 0 || opts->cta_pair < 0 || opts->cta_pair > 2 ||
+            opts->tile_n < 0)
+            return QM_ERR_ARG;
+        if (opts->swap_ab) p.swap_ab = opts->swap_ab - 1;
+        if (opts->tile_n) p.tile_n = opts->tile_n;
+        if (opts->split_k) p.split_k = opts->split_k;
+        if (opts->cta_pair) p.cta_pair = opts->cta_pair;
+    }
+    return tc_launch(g, p, *ctx);
+}
+
+}  // namespace
+
+int record_cuda_error(cudaError_t e, const char *what)
+{
+    t_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return QM_ERR_CUDA;
+}
+
+void nshard_range(int n, int world, int rank, int *begin, int *count)
+{
+    const int unit = (n % 128 == 0 && n / 128 >= world) ? 128 : 1;
+    const int units = n / unit, base = units / world, extra = units % world;
+    const int first_big = world - extra;  // ranks >= first_big carry one more unit
+    const int my_units = base + (rank >= first_big ? 1 : 0);
+    const int my_begin_units = rank * base + (rank > first_big ? rank - first_big : 0);
+    *begin = my_begin_units * unit;
+    *count = my_units * unit;
+}
+
+}  // namespace qm
+
+using namespace qm;
+
+extern "C" {
+
+const char *qm_status_string(int status)
+{
+    switch (status) {
+        case QM_OK: return "QM_OK";
+        case QM_ERR_NULL: return "QM_ERR_NULL: a required pointer is NULL";
+        case QM_ERR_SHAPE: return "QM_ERR_SHAPE: m, n, k must be non-negative, k even, ldc >= n";
+        case QM_ERR_ALIGN: return "QM_ERR_ALIGN: operand alignment not supported by the requested kernel";
+        case QM_ERR_CUDA: return "QM_ERR_CUDA: a CUDA call failed (see qm_last_cuda_error)";
+        case QM_ERR_TIMEOUT: return "QM_ERR_TIMEOUT: a bounded in-kernel wait expired";
+        case QM_ERR_ARCH: return "QM_ERR_ARCH: the current device is not compute capability 10.x";
+        case QM_ERR_WORKSPACE: return "QM_ERR_WORKSPACE: scratch memory too small";
+        case QM_ERR_ARG: return "QM_ERR_ARG: option out of range";
+        default: return "QM_ERR_UNKNOWN";
+    }
+}
+
+int qm_version(void) { return 100; }
+
+const char *qm_last_cuda_error(void) { return t_last_error.c_str(); }
+
+int qm_init(int device)
+{
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return record_cuda_error(e, "cudaGetDevice");
+    if (device != prev && (e = cudaSetDevice(device)) != cudaSuccess) return record_cuda_error(e, "cudaSetDevice");
+    DeviceCtx *ctx = nullptr;
+    int st = ensure_ctx(&ctx);
+    if (device != prev) cudaSetDevice(prev);
+    return st;
+}
+
+int qm_gemm_s4(const void *A, const void *B, void *C, int m, int n, int k, void *stream)
+{
+    return gemm_dispatch(A, B, C, m, n, k, n, stream, nullptr);
+}
+
+int qm_gemm_s4_ex(const void *A, const void *B, void *C, int m, int n, int k, void *stream, const qm_gemm_opts_t *opts)
+{
+    return gemm_dispatch(A, B, C, m, n, k, n, stream, opts);
+}
+
+int qm_gemm_s4_ldc(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc, void *stream)
+{
+    return gemm_dispatch(A, B, C, m, n, k, ldc, stream, nullptr);
+}
+
+int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int k)
+{
+    int st = check_gemm_args(hA, hB, hC, m, n, k, n);
+    if (st != QM_OK) return st;
+    if (m == 0 || n == 0) return QM_OK;
+    DeviceCtx *ctx = nullptr;
+    st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    const size_t a_bytes = (size_t)m * (k / 2), b_bytes = (size_t)n * (k / 2), c_bytes = (size_t)m * n * 4;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    HostStage &s = g_stage[ctx->device];
+    auto grow = [](void *&p, size_t &have, size_t need) -> cudaError_t {
+        if (need <= have) return cudaSuccess;
+        if (p) cudaFree(p);
+        p = nullptr;
+        have = 0;
+        cudaError_t e = cudaMalloc(&p, need);
+        if (e == cudaSuccess) have = need;
+        return e;
+    };
+    cudaError_t e;
+    if ((e = grow(s.a, s.a_bytes, a_bytes ? a_bytes : 16)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(A)");
+    if ((e = grow(s.b, s.b_bytes, b_bytes ? b_bytes : 16)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(B)");
+    if ((e = grow(s.c, s.c_bytes, c_bytes)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(C)");
+    cudaStream_t stream = cudaStreamPerThread;
+    if (a_bytes && (e = cudaMemcpyAsync(s.a, hA, a_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpyAsync(A)");
+    if (b_bytes && (e = cudaMemcpyAsync(s.b, hB, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpyAsync(B)");
+    st = gemm_dispatch(s.a, s.b, s.c, m, n, k, n, stream, nullptr);
+    if (st != QM_OK) return st;
+    if ((e = cudaMemcpyAsync(hC, s.c, c_bytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpyAsync(C)");
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return record_cuda_error(e, "cudaStreamSynchronize");
+    int code = 0;
+    if ((e = cudaMemcpy(&code, ctx->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpy(status)");
+    return code;
+}
+
+int qm_pack_s4(const void *in_s8, void *out_packed, int64_t rows, int64_t k, void *stream)
+{
+    if (rows < 0 || k < 0 || (k & 1)) return QM_ERR_SHAPE;
+    if (rows == 0 || k == 0) return QM_OK;
+    if (!in_s8 || !out_packed) return QM_ERR_NULL;
+    return pack_launch(static_cast<const int8_t *>(in_s8), static_cast<uint8_t *>(out_packed), rows, k,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int qm_unpack_s4(const void *in_packed, void *out_s8, int64_t rows, int64_t k, void *stream)
+{
+    if (rows < 0 || k < 0 || (k & 1)) return QM_ERR_SHAPE;
+    if (rows == 0 || k == 0) return QM_OK;
+    if (!in_packed || !out_s8) return QM_ERR_NULL;
+    return unpack_launch(static_cast<const uint8_t *>(in_packed), static_cast<int8_t *>(out_s8), rows, k,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int qm_fill_s4(void *out_packed, int64_t rows, int64_t k, uint64_t seed, void *stream)
+{
+    if (rows < 0 || k < 0 || (k & 1)) return QM_ERR_SHAPE;
+    if (rows == 0 || k == 0) return QM_OK;
+    if (!out_packed) return QM_ERR_NULL;
+    return fill_launch(static_cast<uint8_t *>(out_packed), rows, k, seed, static_cast<cudaStream_t>(stream));
+}
+
+int qm_nshard_range(int n, int world, int rank, int *begin, int *count)
+{
+    if (!begin || !count) return QM_ERR_NULL;
+    if (n < 0 || world < 1 || rank < 0 || rank >= world) return QM_ERR_ARG;
+    nshard_range(n, world, rank, begin, count);
+    return QM_OK;
+}
+
+int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t slab_stride, void *stream)
+{
+    if (m < 0 || n < 0 || world < 1) return QM_ERR_SHAPE;
+    if (m == 0 || n == 0) return QM_OK;
+    if (!slabs || !C) return QM_ERR_NULL;
+    return unshard_launch(static_cast<const int32_t *>(slabs), static_cast<int32_t *>(C), m, n, world, slab_stride,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int qm_device_status(int *code, int *where, int clear)
+{
+    DeviceCtx *ctx = nullptr;
+    int st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return record_cuda_error(e, "cudaDeviceSynchronize");
+    int words[2] = {0, 0};
+    if ((e = cudaMemcpy(words, ctx->status, sizeof(words), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpy(status)");
+    if (code) *code = words[0];
+    if (where) *where = words[1];
+    if (clear && (e = cudaMemset(ctx->status, 0, sizeof(words))) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemset(status)");
+    return QM_OK;
+}
+
+int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
+{
+    if (!opts) return QM_ERR_NULL;
+    if (m < 0 || n < 0 || k < 0 || (k & 1)) return QM_ERR_SHAPE;
+    std::memset(opts, 0, sizeof(*opts));
+    if (k % 32 != 0 || k >= 131072) {
+        opts->kernel = QM_KERNEL_SIMT;
+        return QM_OK;
+    }
+    TcPlan p = plan_tc(m, n, k, 148);
+    opts->kernel = QM_KERNEL_TC;
+    opts->tile_n = p.tile_n;
+    opts->swap_ab = p.swap_ab + 1;
+    opts->split_k = p.split_k;
+    opts->cta_pair = p.cta_pair;
+    return QM_OK;
+}
+
+}  // extern "C"
+
+// The reference's C++ entry point (extension.cpp:6, kernel.cu:334), same signature and linkage.
+void wrapper(void *A, void *B, void *C, const int m, const int n, const int k, CUstream_st *stream)
+{
+    int st = qm_gemm_s4(A, B, C, m, n, k, stream);
+    if (st != QM_OK) {
+        static int reported_mask = 0;
+        if (!(reported_mask & (1 << st))) {
+            reported_mask |= 1 << st;
+            std::fprintf(stderr, "quadmul_b200: wrapper(m=%d, n=%d, k=%d) failed: %s %s\n", m, n, k, qm_status_string(st),
+                         qm_last_cuda_error());
+        }
+    }
+}

@@ -1,0 +1,75 @@
+// Internal interfaces between the C-ABI layer (qm_api.cu) and the kernel files.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/quadmul_b200.h"
+
+namespace qm {
+
+// Where an in-kernel bounded wait gave up (second word of the device status).
+enum WaitSite : int {
+    kWaitNone = 0,
+    kWaitProducerSlot = 1,   // TMA producer waiting for a free packed stage
+    kWaitConvertPacked = 2,  // converters waiting for TMA data
+    kWaitConvertSlot = 3,    // converters waiting for a free converted stage
+    kWaitMmaAcc = 4,         // MMA issuer waiting for a drained accumulator
+    kWaitMmaOperands = 5,    // MMA issuer waiting for converted operands
+    kWaitEpilogueAcc = 6,    // epilogue waiting for a finished accumulator
+    kWaitSplitK = 7,         // split-K reducer waiting for partial tiles
+    kWaitPeer = 8            // waiting for the peer CTA of a pair
+};
+
+// Per-device state created by qm_init.
+struct DeviceCtx {
+    bool ready = false;
+    int device = -1;
+    int num_sms = 0;
+    int cc_major = 0;
+    int *status = nullptr;         // [2] device words: code, site
+    int32_t *scratch = nullptr;    // split-K partial tiles
+    size_t scratch_bytes = 0;
+    int *counters = nullptr;       // split-K arrival counters (self-resetting, start at zero)
+    int num_counters = 0;
+};
+
+struct GemmArgs {
+    const uint8_t *A;  // M x K/2
+    const uint8_t *B;  // N x K/2
+    int32_t *C;        // M x ldc
+    int m, n, k;
+    int64_t ldc;
+    cudaStream_t stream;
+};
+
+// Resolved tensor-path plan (see qm_tile_table.h for how it is chosen).
+struct TcPlan {
+    int tile_n;    // UMMA N extent: 16, 32, 64, 128, 256
+    int swap_ab;   // 0: C rows on UMMA-M; 1: C columns (B rows) on UMMA-M
+    int split_k;   // >= 1
+    int cta_pair;  // 1 or 2
+};
+
+// qm_gemm_tc.cu
+int tc_prepare_device();  // opt-in shared memory sizes for every instantiation; returns qm_status
+int tc_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
+size_t tc_scratch_bytes_needed(int m, int n, const TcPlan &p);
+int tc_counters_needed(int m, int n, const TcPlan &p);
+
+// qm_gemm_simt.cu
+int simt_launch(const GemmArgs &g);
+
+// qm_pack.cu
+int pack_launch(const int8_t *in, uint8_t *out, int64_t rows, int64_t k, cudaStream_t s);
+int unpack_launch(const uint8_t *in, int8_t *out, int64_t rows, int64_t k, cudaStream_t s);
+int fill_launch(uint8_t *out, int64_t rows, int64_t k, uint64_t seed, cudaStream_t s);
+int unshard_launch(const int32_t *slabs, int32_t *C, int m, int n, int world, int64_t slab_stride, cudaStream_t s);
+
+// qm_api.cu
+// Column split of n over `world` ranks: whole units of 128 columns where n allows, the last ranks
+// take the remainder units.
+void nshard_range(int n, int world, int rank, int *begin, int *count);
+int record_cuda_error(cudaError_t e, const char *what);  // returns QM_ERR_CUDA, stores the text
+
+}  // namespace qm

@@ -1,0 +1,55 @@
+// Shape -> kernel plan for B200.  Replaces the reference's A40-tuned constexpr table
+// (configs.cu:19-689) and its exact-match dispatch chain (kernel.cu:343-384): instead of 42
+// hard-wired (M, N, K) triples and a silent no-op for anything else, every shape resolves to a
+// plan, chosen by the rules below.
+#pragma once
+#include "qm_internal.h"
+
+namespace qm {
+
+struct PlanRule {
+    int m_max;    // rule applies to m <= m_max (rows of C)
+    int swap_ab;  // 1: B rows on the 128-wide UMMA-M axis, tokens on UMMA-N (decode form)
+    int tile_n;   // UMMA N extent
+    int cta_pair; // 1 or 2
+};
+
+// Ordered by m_max.  Decode-sized m puts the weights on the M axis so that a 128-row MMA is fully
+// used by weight rows and only `tile_n` (>= m) columns are spent on tokens.
+static const PlanRule kPlanRules[] = {
+    {16, 1, 16, 1},
+    {32, 1, 32, 1},
+    {64, 1, 64, 1},
+    {128, 1, 128, 1},
+    {0x7FFFFFFF, 0, 256, 1},
+};
+
+inline bool tc_eligible(const GemmArgs &g)
+{
+    auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return g.k % 32 == 0 && g.k < 131072 && aligned16(g.A) && aligned16(g.B);
+}
+
+inline TcPlan plan_tc(int m, int n, int /*k*/, int /*num_sms*/)
+{
+    TcPlan p{256, 0, 1, 1};
+    for (const PlanRule &r : kPlanRules) {
+        if (m <= r.m_max) {
+            p.tile_n = r.tile_n;
+            p.swap_ab = r.swap_ab;
+            p.cta_pair = r.cta_pair;
+            break;
+        }
+    }
+    if (!p.swap_ab) {
+        // narrow outputs: do not spend a 256-wide tile on fewer columns
+        if (n <= 16) p.tile_n = 16;
+        else if (n <= 32) p.tile_n = 32;
+        else if (n <= 64) p.tile_n = 64;
+        else if (n <= 128) p.tile_n = 128;
+        if (p.cta_pair == 2 && p.tile_n < 128) p.cta_pair = 1;
+    }
+    return p;
+}
+
+}  // namespace qm

@@ -1,0 +1,100 @@
+"""The C-ABI library loads without a GPU, exports what include/quadmul_b200.h declares, and rejects
+bad arguments before touching CUDA (CPU only; no compute calls)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "quadmul_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(qm):
+    from quadmul_b200 import _lib
+
+    names = _declared()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(_lib.LIB, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert hasattr(_lib.LIB, _lib.WRAPPER_MANGLED), "C++ symbol wrapper(void*,void*,void*,int,int,int,cudaStream_t) missing"
+
+
+def test_status_strings(qm):
+    from quadmul_b200 import _lib
+
+    assert _lib.LIB.qm_status_string(0) == b"QM_OK"
+    for s in range(1, 9):
+        assert _lib.LIB.qm_status_string(s).startswith(b"QM_ERR_")
+    assert _lib.LIB.qm_version() >= 100
+
+
+def test_argument_errors_do_not_need_a_gpu(qm):
+    from quadmul_b200 import _lib
+
+    L = _lib.LIB
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    assert L.qm_gemm_s4(p, p, p, 4, 4, 7, None) == 2      # k odd
+    assert L.qm_gemm_s4(p, p, p, -1, 4, 8, None) == 2     # negative m
+    assert L.qm_gemm_s4(None, p, p, 4, 4, 8, None) == 1   # NULL A
+    assert L.qm_gemm_s4(p, p, None, 4, 4, 8, None) == 1   # NULL C
+    assert L.qm_gemm_s4(p, p, p, 0, 4, 8, None) == 0      # empty product: nothing to do
+    assert L.qm_gemm_s4(p, p, p, 4, 0, 8, None) == 0
+    assert L.qm_gemm_s4_ldc(p, p, p, 4, 4, 8, 3, None) == 2  # ldc < n
+    assert L.qm_pack_s4(p, p, 2, 3, None) == 2
+    assert L.qm_pack_s4(None, p, 2, 4, None) == 1
+    assert L.qm_pack_s4(None, None, 0, 4, None) == 0
+    assert L.qm_unpack_s4(p, None, 2, 4, None) == 1
+    assert L.qm_fill_s4(None, 2, 4, 1, None) == 1
+    assert L.qm_gemm_s4_host(p, p, p, 2, 2, 3) == 2
+
+
+def test_nshard_range_partitions(qm):
+    for n, world in [(32768, 1), (32768, 2), (32768, 8), (11008, 4), (4096, 8), (1000, 3), (256, 8), (7, 8), (0, 2)]:
+        pos = 0
+        for r in range(world):
+            b, c = qm.nshard_range(n, world, r)
+            assert b == pos and c >= 0
+            pos += c
+        assert pos == n
+    b, c = qm.nshard_range(32768, 8, 3)
+    assert (b, c) == (12288, 4096)
+    # whole 128-column units where n allows
+    assert all(qm.nshard_range(11008, 4, r)[1] % 128 == 0 for r in range(4))
+    with pytest.raises(qm.QuadmulError):
+        qm.nshard_range(128, 4, 4)
+
+
+def test_plan(qm):
+    from quadmul_b200 import _lib
+
+    p = qm.plan(8192, 8192, 8192)
+    assert p["kernel"] == _lib.QM_KERNEL_TC and p["tile_n"] == 256 and p["swap_ab"] == 1
+    d = qm.plan(16, 4096, 4096)
+    assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16
+    assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
+    assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
+    with pytest.raises(qm.QuadmulError):
+        qm.plan(4, 4, 3)
+
+
+def test_python_mirror_checks_arguments(qm):
+    import torch
+
+    a = torch.zeros((4, 4), dtype=torch.int8)
+    c = torch.zeros((4, 4), dtype=torch.int32)
+    with pytest.raises(ValueError):
+        qm.gemm(a, a, c, 4, 4, 8)  # CPU tensors are not accepted: there is no CPU path
+
+
+def test_drop_in_module_name():
+    import quadmul
+
+    assert callable(quadmul.gemm) and callable(quadmul.pack_b)

@@ -1,0 +1,252 @@
+"""Parity of the CUDA GEMM with the oracle, through the C ABI (qm_gemm_s4 / qm_gemm_s4_ex).
+
+Bar: bit-exact int32.  Small and medium sizes are compared in full against the CPU oracle and the
+golden fixtures; the largest sizes through row slabs, sampled points and size-independent
+properties (agreement between independent kernels, linearity in the operands)."""
+import numpy as np
+import pytest
+
+from _util import mismatch_report, run_gemm, to_dev
+
+pytestmark = pytest.mark.gpu
+
+SIMT = dict(kernel=2)
+
+
+def tc(tile_n=0, swap_ab=0, cta_pair=0, split_k=0):
+    return dict(kernel=1, tile_n=tile_n, swap_ab=swap_ab, cta_pair=cta_pair, split_k=split_k)
+
+
+def _check(qm, torch, oracle, ap, bp, want=None, **opts):
+    got = run_gemm(qm, torch, ap, bp, **opts)
+    want = oracle.gemm(ap, bp) if want is None else want
+    assert np.array_equal(got, want), f"opts={opts}: " + mismatch_report(got, want)
+
+
+# ------------------------------------------------------------------ golden fixtures
+def test_golden_auto(qm, cuda_clean, golden):
+    for name, g in golden.items():
+        got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"])
+        assert np.array_equal(got, g["c"]), name + ": " + mismatch_report(got, g["c"])
+
+
+def test_golden_simt(qm, cuda_clean, golden):
+    for name, g in golden.items():
+        got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **SIMT)
+        assert np.array_equal(got, g["c"]), name + ": " + mismatch_report(got, g["c"])
+
+
+@pytest.mark.parametrize("tile_n", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("swap_ab", [1, 2])
+def test_golden_tc_every_tile(qm, cuda_clean, golden, tile_n, swap_ab):
+    if swap_ab == 2 and tile_n == 256:
+        pytest.skip("not instantiated")
+    for name, g in golden.items():
+        got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **tc(tile_n, swap_ab, 1))
+        assert np.array_equal(got, g["c"]), f"{name} tile_n={tile_n} swap={swap_ab}: " + mismatch_report(got, g["c"])
+
+
+# ------------------------------------------------------------------ seeded random shapes
+@pytest.mark.parametrize(
+    "m,n,k",
+    [
+        (1024, 1024, 1024),  # reference-runnable square case
+        (1, 4096, 4096), (16, 4096, 4096), (64, 4096, 4096),  # decode
+        (1, 11008, 4096), (16, 11008, 4096), (64, 11008, 4096),
+        (129, 257, 160), (300, 520, 1056), (127, 1000, 96), (257, 8, 32), (3, 3, 32),  # ragged
+    ],
+)
+def test_random_vs_oracle(qm, cuda_clean, oracle, m, n, k):
+    ap = oracle.fill_packed(m, k, 1000 + m)
+    bp = oracle.fill_packed(n, k, 2000 + n)
+    _check(qm, cuda_clean, oracle, ap, bp)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (12288, 4096), (22016, 4096), (4096, 11008)])
+def test_prefill_shapes(qm, cuda_clean, oracle, n, k):
+    m = 2048
+    ap = oracle.fill_packed(m, k, 31)
+    bp = oracle.fill_packed(n, k, 32)
+    _check(qm, cuda_clean, oracle, ap, bp)
+
+
+def test_square_1024_every_kernel_agrees(qm, cuda_clean, oracle):
+    ap = oracle.fill_packed(1024, 1024, 1001)
+    bp = oracle.fill_packed(1024, 1024, 2001)
+    want = oracle.gemm(ap, bp)
+    for opts in (SIMT, tc(256, 1, 1), tc(128, 1, 1), tc(64, 1, 1), tc(128, 2, 1), tc(64, 2, 1)):
+        _check(qm, cuda_clean, oracle, ap, bp, want=want, **opts)
+
+
+# ------------------------------------------------------------------ edge cases
+def test_empty_and_k_zero(qm, cuda_clean):
+    torch = cuda_clean
+    a = torch.zeros((4, 16), dtype=torch.int8, device="cuda")
+    c = torch.full((4, 4), 7, dtype=torch.int32, device="cuda")
+    qm.gemm(a, a, c, 0, 4, 32)  # no rows: nothing written
+    qm.gemm(a, a, c, 4, 0, 32)
+    assert (c == 7).all()
+    qm.gemm(a, a, c, 4, 4, 0)   # empty sum
+    torch.cuda.synchronize()
+    assert (c == 0).all()
+
+
+def test_extreme_values_long_k(qm, cuda_clean, oracle):
+    # all -8 x all -8 is the largest sum; K = 131040 is the largest the tensor path takes (256 * 64 * K < 2^31)
+    k = 131040
+    a = np.full((130, k), -8, np.int8)
+    b = np.full((40, k), -8, np.int8)
+    b[1::2] = 7
+    ap, bp = oracle.pack(a), oracle.pack(b)
+    want = np.empty((130, 40), np.int32)
+    want[:, 0::2] = 64 * k
+    want[:, 1::2] = -56 * k
+    for opts in (tc(64, 1, 1), tc(32, 2, 1), {}):
+        _check(qm, cuda_clean, oracle, ap, bp, want=want, **opts)
+
+
+def test_k_not_multiple_of_32_and_huge_k_take_the_dp4a_kernel(qm, cuda_clean, oracle):
+    for m, n, k in [(5, 7, 30), (33, 65, 2), (70, 70, 1002)]:
+        ap = oracle.pack(oracle.random_s4(m, k, 5)); bp = oracle.pack(oracle.random_s4(n, k, 6))
+        _check(qm, cuda_clean, oracle, ap, bp)
+    k = 131072 + 64
+    a = np.full((3, k), -8, np.int8); b = np.full((5, k), -8, np.int8)
+    want = np.full((3, 5), 64 * k, np.int32)
+    _check(qm, cuda_clean, oracle, oracle.pack(a), oracle.pack(b), want=want)
+
+
+def test_unaligned_operands(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    m, n, k = 20, 36, 64
+    ap = oracle.pack(oracle.random_s4(m, k, 8)); bp = oracle.pack(oracle.random_s4(n, k, 9))
+    want = oracle.gemm(ap, bp)
+    abuf = torch.zeros(ap.size + 16, dtype=torch.int8, device="cuda")
+    a = abuf[1 : 1 + ap.size].view(m, k // 2)  # 1 byte off a 16-byte boundary
+    a.copy_(to_dev(torch, ap))
+    b = to_dev(torch, bp)
+    c = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize()
+    assert np.array_equal(c.cpu().numpy(), want)
+    from quadmul_b200 import QuadmulError
+
+    with pytest.raises(QuadmulError):
+        qm.gemm_ex(a, b, c, m, n, k, kernel=1)  # the tensor path refuses it instead of faulting
+
+
+def test_ldc_writes_a_column_slab(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    from quadmul_b200 import _lib
+
+    m, n, k, ldc, off = 130, 256, 256, 640, 128
+    ap = oracle.fill_packed(m, k, 3); bp = oracle.fill_packed(n, k, 4)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    c = torch.full((m, ldc), -5, dtype=torch.int32, device="cuda")
+    st = _lib.LIB.qm_gemm_s4_ldc(a.data_ptr(), b.data_ptr(), c.data_ptr() + 4 * off, m, n, k, ldc, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    got = c.cpu().numpy()
+    assert np.array_equal(got[:, off : off + n], oracle.gemm(ap, bp))
+    assert (got[:, :off] == -5).all() and (got[:, off + n :] == -5).all()
+
+
+def test_host_buffer_entry_point(qm, cuda_clean, oracle):
+    m, n, k = 96, 200, 512
+    ap = oracle.fill_packed(m, k, 11); bp = oracle.fill_packed(n, k, 12)
+    c = np.zeros((m, n), np.int32)
+    qm.gemm_host(ap, bp, c, m, n, k)
+    assert np.array_equal(c, oracle.gemm(ap, bp))
+
+
+def test_wrapper_symbol_and_current_stream(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    from quadmul_b200 import _lib
+
+    m, n, k = 64, 128, 128
+    ap = oracle.fill_packed(m, k, 13); bp = oracle.fill_packed(n, k, 14)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    c = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        getattr(_lib.LIB, _lib.WRAPPER_MANGLED)(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, s.cuda_stream)
+    s.synchronize()
+    assert np.array_equal(c.cpu().numpy(), oracle.gemm(ap, bp))
+
+
+def test_cuda_graph_capture(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    m, n, k = 256, 512, 512
+    ap = oracle.fill_packed(m, k, 15); bp = oracle.fill_packed(n, k, 16)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    c = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    qm.init()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(3):
+            qm.gemm(a, b, c, m, n, k)  # as the reference's benchmark captures it (test.py:78-81)
+    c.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(c.cpu().numpy(), oracle.gemm(ap, bp))
+
+
+# ------------------------------------------------------------------ full-size configs
+def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    m = n = k = 8192
+    a = qm.fill_packed(m, k, 1002); b = qm.fill_packed(n, k, 2002)
+    c = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize()
+    ap = a.cpu().numpy().view(np.uint8); bp = b.cpu().numpy().view(np.uint8)
+    assert np.array_equal(ap[:64], oracle.fill_packed(64, k, 1002))  # device generator = oracle generator
+    # (1) row slabs against the oracle, in full
+    for m0 in (0, 4032, 8192 - 96):
+        want = oracle.gemm(ap, bp, rows=(m0, m0 + 96))
+        got = c[m0 : m0 + 96].cpu().numpy()
+        assert np.array_equal(got, want), mismatch_report(got, want)
+    # (2) random points
+    rng = np.random.default_rng(0)
+    rows = rng.integers(0, m, 4096); cols = rng.integers(0, n, 4096)
+    got = c[torch.from_numpy(rows).cuda(), torch.from_numpy(cols).cuda()].cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, oracle.gemm_points(ap, bp, rows, cols))
+    # (3) the whole matrix against an independent GPU computation: unpack kernel + cuBLASLt int8
+    ref = torch._int_mm(qm.unpack(a), qm.unpack(b).t())
+    assert torch.equal(c, ref)
+    # (4) linearity in A: with A' = A clamped to [-7, 7], C(-A', B) = -C(A', B)
+    ua = qm.unpack(a).clamp_(min=-7)
+    c_pos = torch.empty_like(c); c_neg = torch.empty_like(c)
+    qm.gemm(qm.pack(ua), b, c_pos, m, n, k)
+    qm.gemm(qm.pack(-ua), b, c_neg, m, n, k)
+    torch.cuda.synchronize()
+    assert torch.equal(c_pos, -c_neg)
+    del ua, c_pos, c_neg, ref
+    # (5) a second kernel family on the same operands
+    c2 = torch.empty_like(c)
+    qm.gemm_ex(a, b, c2, m, n, k, kernel=1, tile_n=128, swap_ab=1, cta_pair=1)
+    torch.cuda.synchronize()
+    assert torch.equal(c, c2)
+
+
+def test_large_32768_sampled(qm, cuda_clean, oracle):
+    torch = cuda_clean
+    m = n = k = 32768
+    free, _ = torch.cuda.mem_get_info()
+    if free < 12 * 2**30:
+        pytest.skip("not enough free device memory")
+    a = qm.fill_packed(m, k, 1005); b = qm.fill_packed(n, k, 2005)
+    c = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize()
+    ap = a.cpu().numpy().view(np.uint8); bp = b.cpu().numpy().view(np.uint8)
+    rng = np.random.default_rng(1)
+    # random points, tile corners and the last row/column
+    rows = np.concatenate([rng.integers(0, m, 2048), np.arange(0, m, 128)[:256], np.arange(127, m, 128)[:256], [m - 1] * 4])
+    cols = np.concatenate([rng.integers(0, n, 2048), np.arange(0, n, 256)[:128].repeat(2), np.arange(255, n, 256)[:128].repeat(2), [0, 255, 256, n - 1]])
+    got = c[torch.from_numpy(rows).cuda(), torch.from_numpy(cols).cuda()].cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, oracle.gemm_points(ap, bp, rows, cols))
+    # one full row and one full column
+    want_row = oracle.gemm(ap[12345:12346], bp)[0]
+    assert np.array_equal(c[12345].cpu().numpy(), want_row)
+    want_col = oracle.gemm(ap, bp[777:778])[:, 0]
+    assert np.array_equal(c[:, 777].cpu().numpy(), want_col)
