@@ -1,0 +1,110 @@
+"""Column-sharded multi-GPU GEMM: one process per GPU, B split by output columns, A replicated.
+
+The reference is single-GPU (one kernel launch, kernel.cu:268-289); this driver is the multi-GPU
+form of the same product.  Output columns are independent, so rank r of `world` owns the contiguous
+block of B rows [begin, begin + count) given by qm_nshard_range (no repacking: a block of rows of
+the packed N x K/2 matrix is itself a packed matrix) and computes the column slab
+C[:, begin:begin+count].  The GEMM needs no communication.  Only when the caller asks for the full
+C does a collective run: an all-gather of the (padded) slabs over NCCL, followed by one kernel that
+un-interleaves [world][m][stride] into row-major C[m][n].
+
+`gemm_fn` / `unshard_fn` default to the CUDA entry points; the CPU tests inject stand-ins so the
+partition, padding and assembly logic runs under the gloo backend.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+
+class NShardedGemm:
+    def __init__(self, n: int, *, world: Optional[int] = None, rank: Optional[int] = None, group=None,
+                 gemm_fn: Optional[Callable] = None, unshard_fn: Optional[Callable] = None):
+        import torch.distributed as dist
+
+        from . import nshard_range
+
+        self.group = group
+        if world is None or rank is None:
+            if not dist.is_initialized():
+                raise RuntimeError("NShardedGemm: pass world and rank, or initialise torch.distributed first")
+            world = dist.get_world_size(group)
+            rank = dist.get_rank(group)
+        if not (0 <= rank < world):
+            raise ValueError("NShardedGemm: rank outside [0, world)")
+        self.n, self.world, self.rank = int(n), int(world), int(rank)
+        self.ranges = [nshard_range(self.n, self.world, r) for r in range(self.world)]
+        self.begin, self.count = self.ranges[self.rank]
+        self.slab_stride = max(c for _, c in self.ranges) if self.ranges else 0
+        self._gemm_fn = gemm_fn
+        self._unshard_fn = unshard_fn
+
+    # -- partition ---------------------------------------------------------------------
+    def shard_of(self, b_full):
+        """This rank's rows of a full packed B (a view, no copy)."""
+        if b_full.shape[0] != self.n:
+            raise ValueError(f"B has {b_full.shape[0]} rows, expected {self.n}")
+        return b_full[self.begin : self.begin + self.count]
+
+    # -- local product -----------------------------------------------------------------
+    def local(self, a, b_shard, m: int, k: int, out=None):
+        """C[:, begin:begin+count] = A @ b_shard^T on this rank's device. `out` may be a padded
+        [m, slab_stride] buffer; the slab is written into its first `count` columns."""
+        import torch
+
+        if b_shard.shape[0] != self.count:
+            raise ValueError(f"rank {self.rank}: B shard has {b_shard.shape[0]} rows, expected {self.count}")
+        if out is None:
+            out = torch.empty((m, self.count), dtype=torch.int32, device=a.device)
+        if out.shape[0] != m or out.shape[1] < self.count:
+            raise ValueError("output slab too small")
+        if self.count == 0 or m == 0:
+            return out
+        if self._gemm_fn is not None:
+            self._gemm_fn(a, b_shard, out, m, self.count, k)
+        else:
+            self._gemm_ldc(a, b_shard, out, m, k)
+        return out
+
+    def _gemm_ldc(self, a, b_shard, out, m, k):
+        import quadmul_b200 as qm
+        from ._lib import LIB, check
+
+        if not (a.is_cuda and b_shard.is_cuda and out.is_cuda):
+            raise ValueError("NShardedGemm.local: CUDA tensors required (there is no CPU path)")
+        if out.stride(1) != 1 or not a.is_contiguous() or not b_shard.is_contiguous():
+            raise ValueError("NShardedGemm.local: operands must be contiguous, out row-major")
+        with qm._on_device(a):
+            st = LIB.qm_gemm_s4_ldc(a.data_ptr(), b_shard.data_ptr(), out.data_ptr(), m, self.count, k, out.stride(0),
+                                    qm._stream_of(a))
+        check(st, f"sharded gemm rank {self.rank}")
+        qm._launches += 1
+
+    # -- optional collective -------------------------------------------------------------
+    def gather(self, slab, m: int, out=None):
+        """Full row-major C[m, n] on every rank from the per-rank column slabs (all-gather + one
+        un-interleave kernel).  `slab` is [m, count] or a padded [m, slab_stride] buffer."""
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            full = slab[:, : self.count]
+            if out is not None:
+                out.copy_(full)
+                return out
+            return full.contiguous()
+        if slab.shape[1] != self.slab_stride:
+            padded = torch.zeros((m, self.slab_stride), dtype=slab.dtype, device=slab.device)
+            padded[:, : self.count] = slab[:, : self.count]
+            slab = padded
+        slab = slab.contiguous()
+        slabs = torch.empty((self.world, m, self.slab_stride), dtype=slab.dtype, device=slab.device)
+        dist.all_gather_into_tensor(slabs.view(-1), slab.view(-1), group=self.group)
+        if out is None:
+            out = torch.empty((m, self.n), dtype=slab.dtype, device=slab.device)
+        if self._unshard_fn is not None:
+            self._unshard_fn(slabs, out, m, self.n, self.world, self.slab_stride)
+        else:
+            from . import unshard_c
+
+            unshard_c(slabs, out, m, self.n, self.world, self.slab_stride)
+        return out
