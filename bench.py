@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the int4 GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+One "step" is one int4 GEMM with M = K = 8192 and N = 8192 columns PER GPU: at N GPUs the problem
+is C[8192, 8192*N] = A[8192, 8192] * B[8192*N, 8192]^T with B split by output columns, A replicated
+and no collective on the data path (weak scaling).  Inputs are seeded synthetic nibbles, uniform on
+[-8, 7].  The metric is TOPS = 2*M*N*K / time, whole job.
+
+The line printed by rank 0 carries, beside the base keys:
+  roofline      the GEMM kernel against the dense int8 tensor peak (2 x the measured bf16 rate)
+  cpu_baseline  the CPU oracle timed on a bounded row slab of the same product (N=1 only)
+  e2e           the same metric through the host-buffer C-ABI call, copies included
+  clocks        SM clock and throttle reasons sampled during the timed region
+
+`--impl reference` times the reference's own CPU implementation of the path (its compiled
+cpu_gemm_int8 + unpack_int4_matrix where that build exists, else the oracle port) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import socket
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = K = 8192
+N_PER_GPU = 8192
+METRIC = "int4 GEMM TOPS at M=N=K=8192"
+UNIT = "TOPS"
+INT8_PEAK_NOMINAL_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
+FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of gemm_tc_kernel, from the ncu
+# capture summarised in profiles/gemm_tc_8192.md (None until that capture exists)
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def config(n_gpus: int) -> dict:
+    return {
+        "workload": f"int4 GEMM M={M} K={K}, N={N_PER_GPU} per GPU ({N_PER_GPU * n_gpus} total; B column-sharded, A replicated)",
+        "m": M,
+        "n_total": N_PER_GPU * n_gpus,
+        "k": K,
+        "values": "uniform on [-8, 7], seeded",
+        "parallelism": f"n-shard x{n_gpus}, no data-path collective",
+        "l2": "working set 320 MiB per GPU exceeds the 126 MB L2; the 256 MiB C is rewritten every step",
+    }
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            bf16 = float(json.load(f)["bf16_tflops"])
+        return 2.0 * bf16, "2 x measured bf16_tflops (burst) from MEASURED_PEAKS.json; int8 issues at twice the bf16 rate"
+    except Exception:
+        return 2.0 * FALLBACK_BF16_TFLOPS, "2 x fallback bf16 figure (MEASURED_PEAKS.json absent)"
+
+
+# ------------------------------------------------------------------------------------------
+# clocks: read-only NVML polling in a thread
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._ok = False
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self._ok = True
+        except Exception:
+            self._ok = False
+
+    _REASONS = {
+        "hw_slowdown": 0x8,
+        "sw_power_cap": 0x4,
+        "sw_thermal_slowdown": 0x20,
+        "hw_thermal_slowdown": 0x40,
+        "hw_power_brake_slowdown": 0x80,
+    }
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                for name, bit in self._REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._ok:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ------------------------------------------------------------------------------------------
+# CPU legs (the only places that touch oracle/)
+# ------------------------------------------------------------------------------------------
+def cpu_baseline_port(rows: int = 1024) -> dict:
+    """The oracle (CPU restatement, OpenMP) on rows [0, rows) of the 8192^3 product."""
+    from oracle import oracle as o
+
+    a = o.fill_packed(rows, K, 1002)
+    b = o.fill_packed(N_PER_GPU, K, 2002)
+    o.gemm(a[:8], b)  # warm the threads
+    t0 = time.perf_counter()
+    o.gemm(a, b)
+    dt = time.perf_counter() - t0
+    return {
+        "value": 2.0 * rows * N_PER_GPU * K / dt / 1e12,
+        "unit": UNIT,
+        "cores": o.threads(),
+        "kind": "port",
+        "sample": f"rows 0..{rows - 1} of the 8192^3 product ({rows}/8192 of the work), {dt:.2f} s",
+    }
+
+
+def reference_arm(args) -> None:
+    """The reference's CPU implementation of the path on the host cores, one bounded slab per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import concurrent.futures as cf
+
+    import numpy as np
+
+    from oracle import oracle as o
+
+    threads = os.cpu_count() or 1
+    use_ref = o.ref_lib() is not None
+    rows_per_thread = 2 if use_ref else 16
+    rows = rows_per_thread * threads
+    ap = o.fill_packed(rows, K, 1002)
+    bp = o.fill_packed(N_PER_GPU, K, 2002)
+    if use_ref:
+        # kernel.cu:389-408 then kernel.cu:291-306, as compiled from the reference's sources; the
+        # reference code is single-threaded, so row slabs run on a thread pool (ctypes drops the GIL)
+        bu = o.ref_unpack(bp)
+
+        def one(i):
+            sl = ap[i * rows_per_thread : (i + 1) * rows_per_thread]
+            return o.ref_cpu_gemm(o.ref_unpack(sl), bu)
+
+        pool = cf.ThreadPoolExecutor(max_workers=threads)
+
+        def step():
+            list(pool.map(one, range(threads)))
+
+        kind = "reference"
+    else:
+        o.set_threads(threads)
+
+        def step():
+            o.gemm(ap, bp)
+
+        kind = "port"
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 2.0 * rows * N_PER_GPU * K / dt / 1e12
+    sample = f"{rows} rows of the 8192^3 product per step ({rows_per_thread} per thread, {threads} threads)"
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": dt * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "s4 x s4 -> s32 (CPU int32 multiply-add)",
+        "data": "synthetic",
+        "config": config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# native arm
+# ------------------------------------------------------------------------------------------
+def free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def native_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import quadmul_b200 as qm
+    from quadmul_b200.sharded import NShardedGemm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the native arm has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    qm.init()
+
+    n_total = N_PER_GPU * world
+    sh = NShardedGemm(n_total, world=world, rank=rank)
+    a = qm.fill_packed(M, K, 1002)                       # replicated
+    b = qm.fill_packed(sh.count, K, 2002 + 7919 * rank)  # this rank's rows of B
+    c = torch.empty((M, sh.count), dtype=torch.int32, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        sh.local(a, b, M, K, out=c)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    launches_before = qm.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        step()
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    gpu_launches = qm.launch_count() - launches_before
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    code, where = qm.device_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: in-kernel wait expired (site {where & 0xFF}); no number reported")
+
+    ops_per_gpu = 2.0 * M * sh.count * K
+    ms_per_step = total_ms / args.steps
+    value = ops_per_gpu * world / (ms_per_step * 1e-3) / 1e12
+
+    line = None
+    if rank == 0:
+        peak, peak_note = measured_peaks()
+        avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
+        achieved = ops_per_gpu / (avg_launch_ms * 1e-3) / 1e12
+        roofline = {
+            "kernel": "gemm_tc_kernel<256>",
+            "bound": "tensor",
+            "achieved": achieved,
+            "peak": peak,
+            "unit": "TOP/s",
+            "frac": achieved / peak,
+            "traffic": DRAM_TRAFFIC_BYTES_PER_LAUNCH,
+            "peak_note": peak_note + " (of measured)" if "measured" in peak_note else peak_note + " (of fallback)",
+            "peak_nominal": INT8_PEAK_NOMINAL_TOPS,
+            "frac_nominal": achieved / INT8_PEAK_NOMINAL_TOPS,
+            "launch_ms_min": per_launch_ms[0],
+            "launch_ms_median": per_launch_ms[len(per_launch_ms) // 2],
+            "algorithmic_ops_per_launch": ops_per_gpu,
+            "algorithmic_bytes_per_launch": M * K // 2 + sh.count * K // 2 + 4 * M * sh.count,
+        }
+        line = {
+            "metric": METRIC,
+            "value": value,
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "s4 x s4 -> s32 (tcgen05 kind::i8, exact)",
+            "data": "synthetic",
+            "config": config(world),
+            "pct_int8_peak_nominal": 100.0 * value / (INT8_PEAK_NOMINAL_TOPS * world),
+            "roofline": roofline,
+            "gpu_launches": gpu_launches,
+            "clocks": clocks,
+        }
+
+    # ---- end to end through the host-buffer C-ABI call, copies inside the timed region ----
+    if rank == 0 or world > 1:
+        ha = a.cpu().pin_memory()
+        hb = b.cpu().pin_memory()
+        hc = torch.empty((M, sh.count), dtype=torch.int32).pin_memory()
+        e2e_steps = max(3, min(10, args.steps))
+        qm.gemm_host(ha, hb, hc, M, sh.count, K)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            qm.gemm_host(ha, hb, hc, M, sh.count, K)
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            line["e2e"] = {
+                "value": ops_per_gpu * world / float(dt.item()) / 1e12,
+                "unit": UNIT,
+                "h2d_bytes_per_step": int(ha.numel() + hb.numel()),
+                "d2h_bytes_per_step": int(hc.numel() * 4),
+                "ms_per_step": float(dt.item()) * 1e3,
+                "steps": e2e_steps,
+                "api": "qm_gemm_s4_host (pinned host A, B in; int32 C out; per GPU)",
+                "result_checksum": int(hc.view(-1)[:: 65537].sum()),
+            }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_port()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if args.gpus > 1 and "RANK" not in os.environ:
+        # started by hand without a launcher: re-enter under torch.distributed.run
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    native_arm(args)
+
+
+if __name__ == "__main__":
+    main()
