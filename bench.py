@@ -60,9 +60,18 @@ def measured_peaks() -> tuple[float, str]:
     try:
         with open(path) as f:
             bf16 = float(json.load(f)["bf16_tflops"])
-        return 2.0 * bf16, "2 x measured bf16_tflops (burst) from MEASURED_PEAKS.json; int8 issues at twice the bf16 rate"
+        return 2.0 * bf16, "2 x measured bf16_tflops (burst) from MEASURED_PEAKS.json; int8 issues at twice the bf16 rate (of measured)"
     except Exception:
-        return 2.0 * FALLBACK_BF16_TFLOPS, "2 x fallback bf16 figure (MEASURED_PEAKS.json absent)"
+        return 2.0 * FALLBACK_BF16_TFLOPS, "2 x fallback bf16 figure, MEASURED_PEAKS.json absent (of fallback)"
+
+
+def measured_hbm() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured hbm_gbs (copy) from MEASURED_PEAKS.json (of measured)"
+    except Exception:
+        return 6650.0, "fallback HBM figure (MEASURED_PEAKS.json absent) (of fallback)"
 
 
 # ------------------------------------------------------------------------------------------
@@ -137,7 +146,7 @@ def physical_gpu_index(local_index: int) -> int:
 # ------------------------------------------------------------------------------------------
 # CPU legs (the only places that touch oracle/)
 # ------------------------------------------------------------------------------------------
-def cpu_baseline_port(rows: int = 1024) -> dict:
+def cpu_baseline_port(rows: int = 4096) -> dict:
     """The oracle (CPU restatement, OpenMP) on rows [0, rows) of the 8192^3 product."""
     from oracle import oracle as o
 
@@ -253,21 +262,59 @@ def native_arm(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     qm.init()
 
-    n_total = N_PER_GPU * world
+    custom = args.shape is not None
+    if custom:
+        if world != 1:
+            raise SystemExit("bench.py: --shape is a single-GPU option")
+        m, n_total, k = (int(x) for x in args.shape.split(","))
+    else:
+        m, n_total, k = M, N_PER_GPU * world, K
+    forced = dict(tile_n=args.tile_n, swap_ab=args.swap_ab, cta_pair=args.cta_pair, split_k=args.split_k)
+    forced = {kk: v for kk, v in forced.items() if v}
     sh = NShardedGemm(n_total, world=world, rank=rank)
-    a = qm.fill_packed(M, K, 1002)                       # replicated
-    b = qm.fill_packed(sh.count, K, 2002 + 7919 * rank)  # this rank's rows of B
-    c = torch.empty((M, sh.count), dtype=torch.int32, device="cuda")
+    n_local = sh.count
+    a = qm.fill_packed(m, k, 1002)  # replicated
+    # B buffers: one for tensor-bound shapes; for small (HBM-bound) ones enough distinct copies that
+    # consecutive launches cannot be served from the 126 MB L2
+    b_bytes = n_local * (k // 2)
+    per_launch_bytes = m * k // 2 + b_bytes + 4 * m * n_local
+    rotate = 1 if per_launch_bytes > 200e6 else min(64, int(2 * 126e6 // max(per_launch_bytes, 1)) + 2)
+    bs = [qm.fill_packed(n_local, k, 2002 + 7919 * rank + 31 * i) for i in range(rotate)]
+    cs = [torch.empty((m, n_local), dtype=torch.int32, device="cuda") for _ in range(rotate)]
+    c = cs[0]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step():
-        sh.local(a, b, M, K, out=c)
+    counter = [0]
 
-    for _ in range(max(args.warmup, 3)):
+    def launch():
+        i = counter[0] % rotate
+        counter[0] += 1
+        if forced:
+            qm.gemm_ex(a, bs[i], cs[i], m, n_local, k, kernel=1, **forced)
+        else:
+            sh.local(a, bs[i], m, k, out=cs[i])
+
+    launches_per_step = 1
+    if args.graph > 0:
+        launches_per_step = args.graph
+        launch()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(launches_per_step):
+                launch()
+
+        def step():
+            graph.replay()
+    else:
+        step = launch
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier()
     sampler = ClockSampler(physical_gpu_index(local))
@@ -280,9 +327,9 @@ def native_arm(args) -> None:
         ev[i + 1].record()
     barrier()
     clocks = sampler.stop()
-    gpu_launches = qm.launch_count() - launches_before
+    gpu_launches = (qm.launch_count() - launches_before) if args.graph == 0 else args.steps * launches_per_step
     total_ms = ev[0].elapsed_time(ev[-1])
-    per_launch_ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    per_step_ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
     t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -291,45 +338,57 @@ def native_arm(args) -> None:
     if code != 0:
         raise SystemExit(f"bench.py: in-kernel wait expired (site {where & 0xFF}); no number reported")
 
-    ops_per_gpu = 2.0 * M * sh.count * K
+    ops_per_launch = 2.0 * m * n_local * k
     ms_per_step = total_ms / args.steps
-    value = ops_per_gpu * world / (ms_per_step * 1e-3) / 1e12
+    value = ops_per_launch * launches_per_step * world / (ms_per_step * 1e-3) / 1e12
 
     line = None
     if rank == 0:
-        peak, peak_note = measured_peaks()
-        avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
-        achieved = ops_per_gpu / (avg_launch_ms * 1e-3) / 1e12
-        roofline = {
-            "kernel": "gemm_tc_kernel<256>",
-            "bound": "tensor",
-            "achieved": achieved,
-            "peak": peak,
-            "unit": "TOP/s",
-            "frac": achieved / peak,
-            "traffic": DRAM_TRAFFIC_BYTES_PER_LAUNCH,
-            "peak_note": peak_note + " (of measured)" if "measured" in peak_note else peak_note + " (of fallback)",
-            "peak_nominal": INT8_PEAK_NOMINAL_TOPS,
-            "frac_nominal": achieved / INT8_PEAK_NOMINAL_TOPS,
-            "launch_ms_min": per_launch_ms[0],
-            "launch_ms_median": per_launch_ms[len(per_launch_ms) // 2],
-            "algorithmic_ops_per_launch": ops_per_gpu,
-            "algorithmic_bytes_per_launch": M * K // 2 + sh.count * K // 2 + 4 * M * sh.count,
-        }
+        plan = qm.plan(m, n_local, k)
+        plan.update(forced)
+        avg_launch_ms = sum(per_step_ms) / len(per_step_ms) / launches_per_step
+        tensor_bound = (ops_per_launch / per_launch_bytes) > 700  # machine balance of B200, int8 ops per HBM byte
+        if tensor_bound:
+            peak, peak_note = measured_peaks()
+            achieved = ops_per_launch / (avg_launch_ms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
+                        "peak_nominal": INT8_PEAK_NOMINAL_TOPS, "frac_nominal": achieved / INT8_PEAK_NOMINAL_TOPS}
+        else:
+            peak, peak_note = measured_hbm()
+            achieved = per_launch_bytes / (avg_launch_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
+        roofline.update({
+            "kernel": f"gemm_tc_kernel<tile_n={plan['tile_n']}, swap_ab={plan['swap_ab'] - 1}, cta_pair={plan['cta_pair']}>",
+            "traffic": DRAM_TRAFFIC_BYTES_PER_LAUNCH if not custom and not forced else None,
+            "peak_note": peak_note,
+            "launch_ms_min": per_step_ms[0] / launches_per_step,
+            "launch_ms_median": per_step_ms[len(per_step_ms) // 2] / launches_per_step,
+            "launch_ms_avg": avg_launch_ms,
+            "algorithmic_ops_per_launch": ops_per_launch,
+            "algorithmic_bytes_per_launch": per_launch_bytes,
+        })
+        cfg = config(world)
+        if custom:
+            cfg.update({"workload": f"int4 GEMM M={m} N={n_total} K={k} (single GPU, not the headline case)", "m": m,
+                        "n_total": n_total, "k": k})
+            if rotate > 1:
+                cfg["l2"] = f"{rotate} distinct B and C buffers in rotation ({rotate * per_launch_bytes / 1e6:.0f} MB) exceed the 126 MB L2"
+        if args.graph:
+            cfg["cuda_graph_launches_per_step"] = launches_per_step
         line = {
-            "metric": METRIC,
+            "metric": METRIC if not custom else f"int4 GEMM TOPS at M={m} N={n_total} K={k}",
             "value": value,
             "unit": UNIT,
             "n_gpus": world,
             "steps": args.steps,
-            "warmup": max(args.warmup, 3),
+            "warmup": warmup,
             "ms_per_step": ms_per_step,
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
             "dtype": "s4 x s4 -> s32 (tcgen05 kind::i8, exact)",
             "data": "synthetic",
-            "config": config(world),
+            "config": cfg,
             "pct_int8_peak_nominal": 100.0 * value / (INT8_PEAK_NOMINAL_TOPS * world),
             "roofline": roofline,
             "gpu_launches": gpu_launches,
@@ -337,23 +396,23 @@ def native_arm(args) -> None:
         }
 
     # ---- end to end through the host-buffer C-ABI call, copies inside the timed region ----
-    if rank == 0 or world > 1:
+    if not args.no_e2e:
         ha = a.cpu().pin_memory()
-        hb = b.cpu().pin_memory()
-        hc = torch.empty((M, sh.count), dtype=torch.int32).pin_memory()
+        hb = bs[0].cpu().pin_memory()
+        hc = torch.empty((m, n_local), dtype=torch.int32).pin_memory()
         e2e_steps = max(3, min(10, args.steps))
-        qm.gemm_host(ha, hb, hc, M, sh.count, K)
+        qm.gemm_host(ha, hb, hc, m, n_local, k)
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            qm.gemm_host(ha, hb, hc, M, sh.count, K)
+            qm.gemm_host(ha, hb, hc, m, n_local, k)
         torch.cuda.synchronize()
         dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         if rank == 0:
             line["e2e"] = {
-                "value": ops_per_gpu * world / float(dt.item()) / 1e12,
+                "value": ops_per_launch * world / float(dt.item()) / 1e12,
                 "unit": UNIT,
                 "h2d_bytes_per_step": int(ha.numel() + hb.numel()),
                 "d2h_bytes_per_step": int(hc.numel() * 4),
@@ -362,8 +421,9 @@ def native_arm(args) -> None:
                 "api": "qm_gemm_s4_host (pinned host A, B in; int32 C out; per GPU)",
                 "result_checksum": int(hc.view(-1)[:: 65537].sum()),
             }
+            line["gpu_launches"] += e2e_steps + 1
 
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not custom and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_port()
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -379,6 +439,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shape", default=None, help="M,N,K of a single-GPU case other than the headline one (profiling, sweeps)")
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--swap-ab", type=int, default=0)
+    ap.add_argument("--cta-pair", type=int, default=0)
+    ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--graph", type=int, default=0, help="capture this many launches per step in one CUDA graph")
     args = ap.parse_args()
 
     if args.impl == "reference":

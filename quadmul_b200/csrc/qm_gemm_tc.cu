@@ -27,6 +27,9 @@
 // teardown (TMEM is always freed).
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
 
@@ -208,7 +211,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             for (int t = unit; t < num_tiles && ok; t += num_units, ++lt) {
                 const int buf = lt & 1;
                 const uint32_t bph = (lt >> 1) & 1u;
-                if (!mbar_wait<G == 2>(acc_empty(buf), bph ^ 1u, abort_flag)) {
+                if (!(G == 2 ? mbar_spin_wait(acc_empty(buf), bph ^ 1u, abort_flag)
+                             : mbar_wait(acc_empty(buf), bph ^ 1u, abort_flag))) {
                     report_timeout(status, kWaitMmaAcc);
                     *abort_flag = 1;
                     break;
@@ -218,7 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % SC;
                     const uint32_t ph = (it / SC) & 1u;
-                    if (!mbar_wait<G == 2>(cv_full(s), ph, abort_flag)) {
+                    if (!(G == 2 ? mbar_spin_wait(cv_full(s), ph, abort_flag) : mbar_wait(cv_full(s), ph, abort_flag))) {
                         report_timeout(status, kWaitMmaOperands);
                         *abort_flag = 1;
                         ok = false;
@@ -252,8 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             tile_coords(t, tilesP, tilesQ, tp, tq);
             const int buf = lt & 1;
             const uint32_t bph = (lt >> 1) & 1u;
-            bool ok = mbar_wait(acc_full(buf), bph, abort_flag);
-            ok = __all_sync(0xFFFFFFFFu, ok);
+            const bool ok = warp_wait<G == 2>(acc_full(buf), bph, abort_flag, lane);
             if (!ok) {
                 if (lane == 0) {
                     report_timeout(status, kWaitEpilogueAcc);
@@ -328,8 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int ps = it % SP, cs = it % SC;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / SC) & 1u;
-                bool w1 = mbar_wait(pk_full(ps), pph, abort_flag);
-                w1 = __all_sync(0xFFFFFFFFu, w1);
+                const bool w1 = warp_wait<false>(pk_full(ps), pph, abort_flag, lane);
                 if (!w1) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertPacked);
@@ -338,8 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                     ok = false;
                     break;
                 }
-                bool w2 = mbar_wait(cv_empty(cs), cph ^ 1u, abort_flag);
-                w2 = __all_sync(0xFFFFFFFFu, w2);
+                const bool w2 = warp_wait<G == 2>(cv_empty(cs), cph ^ 1u, abort_flag, lane);
                 if (!w2) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -443,10 +444,6 @@ int prepare_one()
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          TcCfg<BN, SWAP, G>::kSmemBytes);
     if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(shared memory)");
-    if (G == 2) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, G>, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
-        if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(cluster)");
-    }
     return QM_OK;
 }
 
@@ -469,12 +466,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx)
     const int tilesQ = (rowsQ + BN - 1) / BN;
     const int64_t tiles = (int64_t)tilesP * tilesQ;
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
-    int units = ctx.num_sms / G;
-    if (units < 1) units = 1;
-    if (tiles < units) units = (int)tiles;
-
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(units * G), 1, 1);
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = g.stream;
@@ -488,6 +480,27 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx)
         attr[0].val.clusterDim.z = 1;
         cfg.numAttrs = 1;
     }
+    // The tile list is static, so every CTA (pair) of the grid must be resident at once: a pair that
+    // only starts when another has finished would run its whole share of tiles alone.
+    int units = ctx.num_sms / G;
+    if (G == 2) {
+        static int max_pairs[64] = {0};
+        int &cached = max_pairs[ctx.device & 63];
+        if (cached == 0) {
+            cfg.gridDim = dim3((unsigned)(2 * (ctx.num_sms / 2)), 1, 1);
+            int n = 0;
+            cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, SWAP, G>, &cfg);
+            if (qe != cudaSuccess) return record_cuda_error(qe, "cudaOccupancyMaxActiveClusters");
+            cached = n > 0 ? n : 1;
+            if (std::getenv("QM_LOG"))
+                std::fprintf(stderr, "quadmul_b200: tile_n=%d pair kernel: %d CTA pairs resident at once (%d SMs)\n", BN,
+                             cached, ctx.num_sms);
+        }
+        if (cached < units) units = cached;
+    }
+    if (units < 1) units = 1;
+    if (tiles < units) units = (int)tiles;
+    cfg.gridDim = dim3((unsigned)(units * G), 1, 1);
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAP, G>, tmP, tmQ, g.C, g.ldc, rowsP, rowsQ, g.k,
                                        ctx.status);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc_kernel launch");

@@ -52,7 +52,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta)
         "{\n"
         " .reg .b32 ra;\n"
         " mapa.shared::cluster.u32 ra, %0, %1;\n"
-        " mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n"
+        " mbarrier.arrive.shared::cluster.b64 _, [ra];\n"
         "}\n" ::"r"(bar),
         "r"(cta)
         : "memory");
@@ -111,6 +111,52 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     return true;
+}
+
+// Non-suspending poll with cluster-scope acquire.  For barriers whose arrivals come from the peer
+// CTA of a pair (remote mbarrier.arrive, tcgen05.commit issued by the other SM).
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+{
+    if (mbar_test_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_test_wait_cluster(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > QM_WAIT_LIMIT_NS) return false;
+        }
+    }
+    return true;
+}
+
+// Whole-warp wait with one verdict for all lanes.  kRemote: lane 0 spins without suspending and the
+// shuffle that broadcasts its verdict also orders the other lanes behind its acquire.
+template <bool kRemote>
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane)
+{
+    if constexpr (!kRemote) {
+        const bool ok = mbar_wait(bar, parity, abort_flag);
+        return __all_sync(0xFFFFFFFFu, ok);
+    } else {
+        int ok = 1;
+        if (lane == 0) ok = mbar_spin_wait(bar, parity, abort_flag) ? 1 : 0;
+        return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+    }
 }
 
 // ---- proxy / tcgen05 fences ------------------------------------------------------------
@@ -248,7 +294,7 @@ __device__ __forceinline__ void tmem_ld_wait()
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
 {
     uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
     return v;
 }
 

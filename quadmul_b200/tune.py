@@ -1,0 +1,94 @@
+"""Sweep of the tensor-path variants over a list of shapes; prints one JSON line per (shape, variant).
+
+    python -m quadmul_b200.tune [--shapes M,N,K;M,N,K;...] [--iters 20]
+
+The plan rules in csrc/qm_tile_table.h are written from these measurements (the reference shipped
+its A40 table without the tuner that produced it; reference README.md:13).  Timing: CUDA events
+around CUDA graphs of back-to-back launches, B buffers rotated so that small problems are not
+served from L2, minimum over `iters` replays.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+DEFAULT_SHAPES = [
+    (1024, 1024, 1024), (8192, 8192, 8192),
+    (1, 4096, 4096), (16, 4096, 4096), (64, 4096, 4096), (1, 11008, 4096), (16, 11008, 4096), (64, 11008, 4096),
+    (2048, 12288, 4096), (2048, 4096, 4096), (2048, 22016, 4096), (2048, 4096, 11008),
+]
+
+
+def variants(m: int, n: int):
+    out = []
+    if m <= 256:
+        for tn in (16, 32, 64, 128):
+            if tn >= min(m, 128) or tn == 128:
+                for sk in (1, 2, 4, 8):
+                    out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk))
+    if m > 64:
+        for tn in (128, 256):
+            out.append(dict(tile_n=tn, swap_ab=1, cta_pair=1, split_k=1))
+            out.append(dict(tile_n=tn, swap_ab=1, cta_pair=2, split_k=1))
+    return out
+
+
+def time_variant(qm, torch, m, n, k, opts, iters, per_graph):
+    per_launch_bytes = m * k // 2 + n * k // 2 + 4 * m * n
+    rotate = 1 if per_launch_bytes > 200e6 else min(64, int(2 * 126e6 // per_launch_bytes) + 2)
+    a = qm.fill_packed(m, k, 1)
+    bs = [qm.fill_packed(n, k, 2 + i) for i in range(rotate)]
+    cs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(rotate)]
+    qm.gemm_ex(a, bs[0], cs[0], m, n, k, kernel=1, **opts)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(per_graph):
+            qm.gemm_ex(a, bs[i % rotate], cs[i % rotate], m, n, k, kernel=1, **opts)
+    g.replay()
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / per_graph)
+    code, where = qm.device_status()
+    return best, code
+
+
+def main():
+    import torch
+
+    import quadmul_b200 as qm
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default=None)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    shapes = DEFAULT_SHAPES if not args.shapes else [tuple(int(x) for x in s.split(",")) for s in args.shapes.split(";")]
+    qm.init()
+    for m, n, k in shapes:
+        ops = 2.0 * m * n * k
+        nbytes = m * k // 2 + n * k // 2 + 4 * m * n
+        per_graph = 10 if ops > 1e11 else 50
+        rows = []
+        for opts in variants(m, n):
+            try:
+                ms, code = time_variant(qm, torch, m, n, k, opts, args.iters, per_graph)
+            except qm.QuadmulError as exc:
+                if exc.status == 8:  # variant not built
+                    continue
+                raise
+            rows.append((ms, opts))
+            print(json.dumps({"m": m, "n": n, "k": k, **opts, "us": round(ms * 1e3, 2), "tops": round(ops / ms / 1e9, 1),
+                              "gbs": round(nbytes / ms / 1e6, 1), "status": code}), flush=True)
+        if rows:
+            ms, opts = min(rows, key=lambda r: r[0])
+            print(json.dumps({"best": [m, n, k], **opts, "us": round(ms * 1e3, 2)}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

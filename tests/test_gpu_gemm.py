@@ -46,6 +46,17 @@ def test_golden_tc_every_tile(qm, cuda_clean, golden, tile_n, swap_ab):
         assert np.array_equal(got, g["c"]), f"{name} tile_n={tile_n} swap={swap_ab}: " + mismatch_report(got, g["c"])
 
 
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_golden_and_random_cta_pair(qm, cuda_clean, oracle, golden, tile_n):
+    """Two-CTA MMA (cta_group::2): each CTA of the pair holds 128 rows of A and half of the B tile."""
+    for name, g in golden.items():
+        got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **tc(tile_n, 1, 2))
+        assert np.array_equal(got, g["c"]), f"{name} pair tile_n={tile_n}: " + mismatch_report(got, g["c"])
+    for m, n, k in [(1024, 1024, 1024), (300, 520, 1056), (2048, 4096, 4096), (257, 8, 32)]:
+        ap = oracle.fill_packed(m, k, 41); bp = oracle.fill_packed(n, k, 42)
+        _check(qm, cuda_clean, oracle, ap, bp, **tc(tile_n, 1, 2))
+
+
 # ------------------------------------------------------------------ seeded random shapes
 @pytest.mark.parametrize(
     "m,n,k",
