@@ -15,13 +15,16 @@ struct PlanRule {
 };
 
 // Ordered by m_max.  Decode-sized m puts the weights on the M axis so that a 128-row MMA is fully
-// used by weight rows and only `tile_n` (>= m) columns are spent on tokens.
+// used by weight rows and only `tile_n` (>= m) columns are spent on tokens.  Everything larger runs
+// the 256 x 256 CTA-pair tile: measured on B200 it beats the single-CTA 128 x 256 and both 128-wide
+// forms at 8192^3 and at all four M = 2048 prefill shapes (python -m quadmul_b200.tune), because
+// each SM converts and feeds only half of the B tile.
 static const PlanRule kPlanRules[] = {
     {16, 1, 16, 1},
     {32, 1, 32, 1},
     {64, 1, 64, 1},
     {128, 1, 128, 1},
-    {0x7FFFFFFF, 0, 256, 1},
+    {0x7FFFFFFF, 0, 256, 2},
 };
 
 inline bool tc_eligible(const GemmArgs &g)
