@@ -14,6 +14,8 @@ namespace qm {
 namespace {
 
 constexpr int kMaxDevices = 64;
+constexpr size_t kScratchBytes = 32u << 20;  // split-K partial tiles, per device
+constexpr int kNumCounters = 16384;
 DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mutex;
 thread_local std::string t_last_error;
@@ -48,6 +50,17 @@ int ensure_ctx(DeviceCtx **out)
                 cudaFree(status);
                 return st;
             }
+            // split-K scratch: partial tiles and self-resetting arrival counters (zero between launches)
+            void *scratch = nullptr, *counters = nullptr;
+            if ((e = cudaMalloc(&scratch, kScratchBytes)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(scratch)");
+            if ((e = cudaMalloc(&counters, kNumCounters * sizeof(int))) != cudaSuccess)
+                return record_cuda_error(e, "cudaMalloc(counters)");
+            if ((e = cudaMemset(counters, 0, kNumCounters * sizeof(int))) != cudaSuccess)
+                return record_cuda_error(e, "cudaMemset(counters)");
+            c.scratch = static_cast<int32_t *>(scratch);
+            c.scratch_bytes = kScratchBytes;
+            c.counters = static_cast<int *>(counters);
+            c.num_counters = kNumCounters;
             c.device = dev;
             c.cc_major = major;
             c.num_sms = sms;
@@ -101,6 +114,9 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->split_k) p.split_k = opts->split_k;
         if (opts->cta_pair) p.cta_pair = opts->cta_pair;
     }
+    if (p.split_k > 1 && !(opts && opts->split_k) &&
+        (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
+        p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
     return tc_launch(g, p, *ctx);
 }
 

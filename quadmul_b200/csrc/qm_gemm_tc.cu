@@ -112,7 +112,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 template <int BN, bool SWAP, int G>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
-               int32_t *__restrict__ C, int64_t ldc, int rowsP, int rowsQ, int K, int *status)
+               int32_t *__restrict__ C, int64_t ldc, int rowsP, int rowsQ, int K, int *status, int split_k,
+               int32_t *__restrict__ scratch, int *__restrict__ counters)
 {
     using Cfg = TcCfg<BN, SWAP, G>;
     constexpr int SP = Cfg::SP, SC = Cfg::SC;
@@ -139,8 +140,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 
     const int tilesP = (rowsP + 128 * G - 1) / (128 * G);
     const int tilesQ = (rowsQ + BN - 1) / BN;
-    const int num_tiles = tilesP * tilesQ;
-    const int num_kb = (K + kKBlock - 1) / kKBlock;
+    const int num_kb_total = (K + kKBlock - 1) / kKBlock;
+    // A work item is one K partition of one output tile; partitions of a tile are adjacent items.
+    const int num_tiles = tilesP * tilesQ * split_k;
+    auto kb_begin = [&](int item) { return (int)(((long long)(item % split_k) * num_kb_total) / split_k); };
+    auto kb_end = [&](int item) { return (int)(((long long)(item % split_k + 1) * num_kb_total) / split_k); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SP; ++s) {
@@ -183,10 +187,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             bool ok = true;
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
-                tile_coords(t, tilesP, tilesQ, tp, tq);
+                tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
                 const int yP = tp * 128 * G + (int)cta_rank * 128;
                 const int yQ = tq * BN + (int)cta_rank * Cfg::kRowsQ;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                     const int s = it % SP;
                     const uint32_t ph = (it / SP) & 1u;
                     if (!mbar_wait(pk_empty(s), ph ^ 1u, abort_flag)) {
@@ -219,7 +223,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                 }
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb0 = kb_begin(t);
+                for (int kb = kb0, kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                     const int s = it % SC;
                     const uint32_t ph = (it / SC) & 1u;
                     if (!(G == 2 ? mbar_spin_wait(cv_full(s), ph, abort_flag) : mbar_wait(cv_full(s), ph, abort_flag))) {
@@ -235,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 #pragma unroll
                     for (int k4 = 0; k4 < kKBlock / 32; ++k4) {
                         // +32 bytes of K inside the 128-byte swizzled row = +2 in the address field
-                        umma_i8<G>(tmem_d, dP + 2u * k4, dQ + 2u * k4, Cfg::kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                        umma_i8<G>(tmem_d, dP + 2u * k4, dQ + 2u * k4, Cfg::kIdesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
                     }
                     umma_commit<G>(cv_empty(s));
                     if constexpr (G == 2) umma_commit<G>(mapa_cluster(cv_empty(s), 1));
@@ -253,7 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         uint32_t lt = 0;
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
-            tile_coords(t, tilesP, tilesQ, tp, tq);
+            tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
             const int buf = lt & 1;
             const uint32_t bph = (lt >> 1) & 1u;
             const bool ok = warp_wait<G == 2>(acc_full(buf), bph, abort_flag, lane);
@@ -268,6 +273,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
             const int p = tp * 128 * G + (int)cta_rank * 128 + quarter * 32 + lane;  // index along the UMMA-M operand
             const int q0 = tq * BN;
+            if (split_k > 1) {
+                // Partial tile -> scratch as [column][row] (coalesced), then whichever K partition of the
+                // tile finishes last sums all of them.  Nobody waits: an arrival counter decides who reduces.
+                const int tile = t / split_k;
+                const int row = quarter * 32 + lane;
+                int32_t *mine = scratch + (int64_t)t * (128 * BN);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld_x16(taddr + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) __stcg(mine + (c + j) * 128 + row, (int32_t)v[j] >> 8);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty(buf));  // the accumulator is drained; split-K runs single-CTA
+                // Each warp owns 32 rows of the tile and its own counter, so no warp waits for another.
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    int *ctr = counters + tile * 4 + quarter;
+                    last = (atomicAdd(ctr, 1) == split_k - 1) ? 1 : 0;
+                    if (last) *ctr = 0;  // ready for the next launch
+                }
+                last = __shfl_sync(0xFFFFFFFFu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int32_t *parts = scratch + (int64_t)tile * split_k * (128 * BN);
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        int32_t sum[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) sum[j] = 0;
+                        for (int sk = 0; sk < split_k; ++sk) {
+                            const int32_t *src = parts + (int64_t)sk * (128 * BN) + c * 128 + row;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) sum[j] += __ldcg(src + j * 128);
+                        }
+                        if (p < rowsP) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int q = q0 + c + j;
+                                if (q < rowsQ) {
+                                    if constexpr (SWAP) C[(int64_t)q * ldc + p] = sum[j];
+                                    else C[(int64_t)p * ldc + q] = sum[j];
+                                }
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             if constexpr (!SWAP) {
                 // C[p][q0 + j]: one thread owns one row, 32 consecutive columns per load.
                 int32_t *crow = C + (int64_t)p * ldc + q0;
@@ -328,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         uint32_t it = 0;
         bool ok = true;
         for (int t = unit; t < num_tiles && ok; t += num_units) {
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                 const int ps = it % SP, cs = it % SC;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / SC) & 1u;
                 const bool w1 = warp_wait<false>(pk_full(ps), pph, abort_flag, lane);
@@ -448,7 +507,8 @@ int prepare_one()
 }
 
 template <int BN, bool SWAP, int G>
-int launch_one(const GemmArgs &g, const DeviceCtx &ctx)
+int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *scratch, size_t scratch_bytes, int *counters,
+               int num_counters)
 {
     using Cfg = TcCfg<BN, SWAP, G>;
     const uint8_t *P = SWAP ? g.B : g.A;
@@ -464,8 +524,15 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx)
 
     const int tilesP = (rowsP + 128 * G - 1) / (128 * G);
     const int tilesQ = (rowsQ + BN - 1) / BN;
-    const int64_t tiles = (int64_t)tilesP * tilesQ;
+    const int num_kb = (g.k + kKBlock - 1) / kKBlock;
+    if (split_k < 1 || split_k > num_kb || (split_k > 1 && G != 1)) return QM_ERR_ARG;
+    const int64_t tiles = (int64_t)tilesP * tilesQ * split_k;
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
+    if (split_k > 1) {
+        if ((size_t)tiles * 128 * BN * sizeof(int32_t) > scratch_bytes || (int64_t)tilesP * tilesQ * 4 > num_counters)
+            return QM_ERR_WORKSPACE;
+        if (!scratch || !counters) return QM_ERR_NULL;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
@@ -502,7 +569,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx)
     if (tiles < units) units = (int)tiles;
     cfg.gridDim = dim3((unsigned)(units * G), 1, 1);
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAP, G>, tmP, tmQ, g.C, g.ldc, rowsP, rowsQ, g.k,
-                                       ctx.status);
+                                       ctx.status, split_k, scratch, counters);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc_kernel launch");
     return QM_OK;
 }
@@ -535,15 +602,34 @@ int tc_prepare_device()
 
 int tc_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx)
 {
-    if (p.split_k != 1) return QM_ERR_ARG;
-#define X(BN, SW, G) \
-    if (p.tile_n == BN && (p.swap_ab != 0) == SW && p.cta_pair == G) return launch_one<BN, SW, G>(g, ctx);
+    return tc_launch_with_scratch(g, p, ctx, ctx.scratch, ctx.scratch_bytes, ctx.counters, ctx.num_counters);
+}
+
+int tc_launch_with_scratch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx, int32_t *scratch, size_t scratch_bytes,
+                           int *counters, int num_counters)
+{
+#define X(BN, SW, G)                                                               \
+    if (p.tile_n == BN && (p.swap_ab != 0) == SW && p.cta_pair == G)               \
+        return launch_one<BN, SW, G>(g, ctx, p.split_k, scratch, scratch_bytes, counters, num_counters);
     QM_TC_FOR_EACH(X)
 #undef X
     return QM_ERR_ARG;
 }
 
-size_t tc_scratch_bytes_needed(int, int, const TcPlan &) { return 0; }
-int tc_counters_needed(int, int, const TcPlan &) { return 0; }
+// Scratch a split-K launch needs: one 128 x tile_n int32 partial per (tile, K partition), one counter per tile.
+size_t tc_scratch_bytes_needed(int m, int n, const TcPlan &p)
+{
+    if (p.split_k <= 1) return 0;
+    const int rowsP = p.swap_ab ? n : m, rowsQ = p.swap_ab ? m : n;
+    const int64_t tiles = (int64_t)((rowsP + 127) / 128) * ((rowsQ + p.tile_n - 1) / p.tile_n);
+    return (size_t)tiles * p.split_k * 128 * p.tile_n * sizeof(int32_t);
+}
+
+int tc_counters_needed(int m, int n, const TcPlan &p)
+{
+    if (p.split_k <= 1) return 0;
+    const int rowsP = p.swap_ab ? n : m, rowsQ = p.swap_ab ? m : n;
+    return 4 * ((rowsP + 127) / 128) * ((rowsQ + p.tile_n - 1) / p.tile_n);  // one per 32-row quarter of a tile
+}
 
 }  // namespace qm

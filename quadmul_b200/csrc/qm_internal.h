@@ -54,6 +54,8 @@ struct TcPlan {
 // qm_gemm_tc.cu
 int tc_prepare_device();  // opt-in shared memory sizes for every instantiation; returns qm_status
 int tc_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
+int tc_launch_with_scratch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx, int32_t *scratch, size_t scratch_bytes,
+                           int *counters, int num_counters);
 size_t tc_scratch_bytes_needed(int m, int n, const TcPlan &p);
 int tc_counters_needed(int m, int n, const TcPlan &p);
 

@@ -33,7 +33,7 @@ inline bool tc_eligible(const GemmArgs &g)
     return g.k % 32 == 0 && g.k < 131072 && aligned16(g.A) && aligned16(g.B);
 }
 
-inline TcPlan plan_tc(int m, int n, int /*k*/, int /*num_sms*/)
+inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
     TcPlan p{256, 0, 1, 1};
     for (const PlanRule &r : kPlanRules) {
@@ -43,6 +43,16 @@ inline TcPlan plan_tc(int m, int n, int /*k*/, int /*num_sms*/)
             p.cta_pair = r.cta_pair;
             break;
         }
+    }
+    if (p.swap_ab) {
+        // Decode form: few tiles, long K.  Split K so that the work items about fill the SMs; measured
+        // best at 4 partitions for N = 4096 (32 tiles) and none for N = 11008 (86 tiles).
+        const int tiles = ((n + 127) / 128) * ((m + p.tile_n - 1) / p.tile_n);
+        const int num_kb = (k + 127) / 128;
+        int s = tiles > 0 ? num_sms / tiles : 1;
+        if (s > 4) s = 4;
+        if (s > num_kb / 2) s = num_kb / 2;
+        p.split_k = s < 1 ? 1 : s;
     }
     if (!p.swap_ab) {
         // narrow outputs: do not spend a 256-wide tile on fewer columns

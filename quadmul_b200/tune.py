@@ -24,7 +24,7 @@ def variants(m: int, n: int):
     if m <= 256:
         for tn in (16, 32, 64, 128):
             if tn >= min(m, 128) or tn == 128:
-                for sk in (1, 2, 4, 8):
+                for sk in (1, 2, 3, 4, 6, 8, 16):
                     out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk))
     if m > 64:
         for tn in (128, 256):
@@ -79,7 +79,7 @@ def main():
             try:
                 ms, code = time_variant(qm, torch, m, n, k, opts, args.iters, per_graph)
             except qm.QuadmulError as exc:
-                if exc.status == 8:  # variant not built
+                if exc.status in (7, 8):  # variant not built, or scratch too small for this split
                     continue
                 raise
             rows.append((ms, opts))
