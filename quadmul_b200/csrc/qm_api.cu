@@ -109,6 +109,8 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->swap_ab < 0 || opts->swap_ab > 2 || opts->split_k < 0 || opts->cta_pair < 0 || opts->cta_pair > 2 ||
             opts->tile_n < 0)
             return QM_ERR_ARG;
+        // the table's K split belongs to the table's tile form: an explicit form starts unsplit
+        if (opts->swap_ab || opts->tile_n || opts->cta_pair) p.split_k = 1;
         if (opts->swap_ab) p.swap_ab = opts->swap_ab - 1;
         if (opts->tile_n) p.tile_n = opts->tile_n;
         if (opts->split_k) p.split_k = opts->split_k;
