@@ -133,6 +133,24 @@ int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t sl
  */
 int qm_device_status(int *code, int *where, int clear);
 
+/*
+ * The split-K tensor-core GEMM for callers that must not allocate device memory (a plug-in under a
+ * host framework's memory pool or a fixed device-memory budget, a real-time loop that cannot absorb
+ * an allocation's stall).  It has no counterpart in the reference.  Same product and layouts as qm_gemm_s4
+ * (ldc = n), computed in `split_k` >= 1 partitions of K whose partial tiles are summed through
+ * scratch that lives in file-scope __device__ arrays of the library: no cudaMalloc, no cudaFree,
+ * no allocating library call, on any call.
+ *   Capacity: 8 MiB of partial tiles and 4096 arrival counters, i.e.
+ *   tiles * split_k * 128 * tile_n * 4 bytes <= 8 MiB with tiles = ceil(n/128) * ceil(m/tile_n) for
+ *   m <= 128 (tile_n = 16, 32, 64, 128 >= m), and 4 * tiles <= 4096; QM_ERR_WORKSPACE beyond it.
+ *   Needs k % 32 == 0, k < 131072 and 16-byte-aligned A and B (QM_ERR_ALIGN otherwise).
+ *   The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress) with
+ *   that device current; make that first call outside any stream capture.
+ *   Every call on a device shares the arrays: calls that overlap on the GPU race; order them.
+ */
+int qm_gemm_s4_static_scratch(const void *A, const void *B, void *C, int m, int n, int k, int split_k,
+                              void *stream);
+
 /* What the dispatcher would run for (m, n, k): fills *opts with the resolved choices. */
 int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts);
 

@@ -46,6 +46,7 @@ SIGNATURES = {
     "qm_unshard_c": (_i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
     "qm_device_status": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), _i]),
     "qm_plan": (_i, [_i, _i, _i, ctypes.POINTER(GemmOpts)]),
+    "qm_gemm_s4_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
 }
 
 # the reference's C++ entry point `wrapper(void*, void*, void*, int, int, int, cudaStream_t)`
