@@ -269,7 +269,7 @@ def native_arm(args) -> None:
         m, n_total, k = (int(x) for x in args.shape.split(","))
     else:
         m, n_total, k = M, N_PER_GPU * world, K
-    forced = dict(tile_n=args.tile_n, swap_ab=args.swap_ab, cta_pair=args.cta_pair, split_k=args.split_k)
+    forced = dict(tile_n=args.tile_n, swap_ab=args.swap_ab, cta_pair=args.cta_pair, split_k=args.split_k, a_tmem=args.a_tmem)
     forced = {kk: v for kk, v in forced.items() if v}
     sh = NShardedGemm(n_total, world=world, rank=rank)
     n_local = sh.count
@@ -358,7 +358,8 @@ def native_arm(args) -> None:
             achieved = per_launch_bytes / (avg_launch_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
         roofline.update({
-            "kernel": f"gemm_tc_kernel<tile_n={plan['tile_n']}, swap_ab={plan['swap_ab'] - 1}, cta_pair={plan['cta_pair']}>",
+            "kernel": ("gemm_tc2_kernel<256x256 pair tile, A in TMEM>" if plan.get("a_tmem") == 2 else
+                       f"gemm_tc_kernel<tile_n={plan['tile_n']}, swap_ab={plan['swap_ab'] - 1}, cta_pair={plan['cta_pair']}>"),
             "traffic": DRAM_TRAFFIC_BYTES_PER_LAUNCH if not custom and not forced else None,
             "peak_note": peak_note,
             "launch_ms_min": per_step_ms[0] / launches_per_step,
@@ -445,6 +446,7 @@ def main() -> None:
     ap.add_argument("--swap-ab", type=int, default=0)
     ap.add_argument("--cta-pair", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--a-tmem", type=int, default=0)
     ap.add_argument("--graph", type=int, default=0, help="capture this many launches per step in one CUDA graph")
     args = ap.parse_args()
 

@@ -49,7 +49,9 @@ typedef struct qm_gemm_opts {
     int swap_ab;    /* 0 = table, 1 = C rows on UMMA-M (prefill form), 2 = C columns on UMMA-M  */
     int split_k;    /* 0 = table; >= 1 number of K partitions reduced through scratch memory    */
     int cta_pair;   /* 0 = table, 1 = single-CTA MMA, 2 = two-CTA (cta_group::2) MMA            */
-    int reserved[3];
+    int a_tmem;     /* 0 = table, 1 = operand A from shared memory, 2 = operand A from TMEM
+                       (only with tile_n 256, cta_pair 2, no swap, no split)                    */
+    int reserved[2];
 } qm_gemm_opts_t;
 
 const char *qm_status_string(int status);

@@ -25,7 +25,8 @@ class GemmOpts(ctypes.Structure):
         ("swap_ab", _i),
         ("split_k", _i),
         ("cta_pair", _i),
-        ("reserved", _i * 3),
+        ("a_tmem", _i),
+        ("reserved", _i * 2),
     ]
 
 

@@ -46,6 +46,7 @@ int ensure_ctx(DeviceCtx **out)
             if ((e = cudaMalloc(&status, 2 * sizeof(int))) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(status)");
             if ((e = cudaMemset(status, 0, 2 * sizeof(int))) != cudaSuccess) return record_cuda_error(e, "cudaMemset(status)");
             int st = tc_prepare_device();
+            if (st == QM_OK) st = tc2_prepare_device();
             if (st != QM_OK) {
                 cudaFree(status);
                 return st;
@@ -115,6 +116,13 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->tile_n) p.tile_n = opts->tile_n;
         if (opts->split_k) p.split_k = opts->split_k;
         if (opts->cta_pair) p.cta_pair = opts->cta_pair;
+        if (opts->a_tmem < 0 || opts->a_tmem > 2) return QM_ERR_ARG;
+        if (opts->a_tmem) p.a_tmem = opts->a_tmem - 1;
+        else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->split_k) p.a_tmem = 0;
+    }
+    if (p.a_tmem) {
+        if (p.swap_ab || p.tile_n != 256 || p.cta_pair != 2 || p.split_k != 1) return QM_ERR_ARG;
+        return tc2_launch(g, *ctx);
     }
     if (p.split_k > 1 && !(opts && opts->split_k) &&
         (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
@@ -309,6 +317,7 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
     opts->swap_ab = p.swap_ab + 1;
     opts->split_k = p.split_k;
     opts->cta_pair = p.cta_pair;
+    opts->a_tmem = p.a_tmem + 1;
     return QM_OK;
 }
 

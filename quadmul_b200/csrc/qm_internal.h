@@ -49,6 +49,7 @@ struct TcPlan {
     int swap_ab;   // 0: C rows on UMMA-M; 1: C columns (B rows) on UMMA-M
     int split_k;   // >= 1
     int cta_pair;  // 1 or 2
+    int a_tmem;    // 1: the 256 x 256 pair tile with operand A in TMEM (gemm_tc2_kernel)
 };
 
 // qm_gemm_tc.cu
@@ -58,6 +59,10 @@ int tc_launch_with_scratch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &
                            int *counters, int num_counters);
 size_t tc_scratch_bytes_needed(int m, int n, const TcPlan &p);
 int tc_counters_needed(int m, int n, const TcPlan &p);
+
+// qm_gemm_tc2.cu: 256 x 256 pair tile, A through TMEM
+int tc2_prepare_device();
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx);
 
 // qm_gemm_simt.cu
 int simt_launch(const GemmArgs &g);

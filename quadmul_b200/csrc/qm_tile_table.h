@@ -35,7 +35,7 @@ inline bool tc_eligible(const GemmArgs &g)
 
 inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
-    TcPlan p{256, 0, 1, 1};
+    TcPlan p{256, 0, 1, 1, 0};
     for (const PlanRule &r : kPlanRules) {
         if (m <= r.m_max) {
             p.tile_n = r.tile_n;

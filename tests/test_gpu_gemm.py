@@ -57,6 +57,17 @@ def test_golden_and_random_cta_pair(qm, cuda_clean, oracle, golden, tile_n):
         _check(qm, cuda_clean, oracle, ap, bp, **tc(tile_n, 1, 2))
 
 
+def test_pair_tile_with_a_in_tmem(qm, cuda_clean, oracle, golden):
+    """gemm_tc2_kernel: the converters write int8 A into TMEM (tcgen05.st) and the MMA reads it from there."""
+    opts = dict(kernel=1, tile_n=256, swap_ab=1, cta_pair=2, a_tmem=2)
+    for name, g in golden.items():
+        got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **opts)
+        assert np.array_equal(got, g["c"]), f"{name}: " + mismatch_report(got, g["c"])
+    for m, n, k in [(256, 256, 128), (1024, 1024, 1024), (300, 520, 1056), (2048, 4096, 4096), (257, 8, 32), (513, 1000, 4064)]:
+        ap = oracle.fill_packed(m, k, 61); bp = oracle.fill_packed(n, k, 62)
+        _check(qm, cuda_clean, oracle, ap, bp, **opts)
+
+
 @pytest.mark.parametrize("split_k", [2, 3, 4, 8])
 def test_split_k_through_scratch(qm, cuda_clean, oracle, golden, split_k):
     """K partitions of a tile write partial tiles to scratch; the last one to arrive sums them.
