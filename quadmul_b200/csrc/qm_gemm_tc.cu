@@ -30,6 +30,7 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include "qm_epilogue.cuh"
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
 
@@ -72,7 +73,9 @@ struct TcCfg {
     static constexpr int SP = SP_raw > 8 ? 8 : SP_raw;
     static constexpr int kTmemCols = next_pow2(2 * BN);
     static constexpr int kNumBarriers = 2 * SP + 2 * SC + 4;
-    static constexpr int kSmemBytes = 1024 + SC * kCvStage + SP * kPkStage + kNumBarriers * 8 + 16;
+    static constexpr int kEpiChunk = BN >= 32 ? 32 : 16;  // columns per TMEM load in the row-major epilogue
+    static constexpr int kEpiBytes = SWAP ? 0 : 4 * EpilogueStage<kEpiChunk>::kBytesPerWarp;
+    static constexpr int kSmemBytes = 1024 + SC * kCvStage + SP * kPkStage + kEpiBytes + kNumBarriers * 8 + 16;
     static constexpr int kItems = kRows * 4;  // 16-byte packed chunks per stage
     static constexpr int kItemIters = (kItems + kConvThreads - 1) / kConvThreads;
     static constexpr uint32_t kIdesc = (2u << 4)                      // D format: s32
@@ -122,7 +125,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     const uint32_t raw_u32 = smem_u32(smem_raw);
     const uint32_t cv0 = (raw_u32 + 1023u) & ~1023u;
     const uint32_t pk0 = cv0 + SC * Cfg::kCvStage;
-    const uint32_t bar0 = pk0 + SP * Cfg::kPkStage;
+    const uint32_t epi0 = pk0 + SP * Cfg::kPkStage;  // per-warp transpose buffers of the row-major epilogue
+    const uint32_t bar0 = epi0 + Cfg::kEpiBytes;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
     auto pk_empty = [&](int s) { return bar0 + 8u * (SP + s); };
     auto cv_full = [&](int s) { return bar0 + 8u * (2 * SP + s); };
@@ -328,35 +332,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                 continue;
             }
             if constexpr (!SWAP) {
-                // C[p][q0 + j]: one thread owns one row, 32 consecutive columns per load.
-                int32_t *crow = C + (int64_t)p * ldc + q0;
+                // C[p][q0 + j]: the block arrives one row per lane and leaves as whole row segments.
                 const bool vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && ((ldc & 3) == 0);
-                constexpr int CH = BN >= 32 ? 32 : 16;
+                constexpr int CH = Cfg::kEpiChunk;
+                const uint32_t stage = epi0 + (uint32_t)((warp - kFirstEpiWarp) * EpilogueStage<CH>::kBytesPerWarp);
+                const int row0 = p - lane;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += CH) {
                     uint32_t v[CH];
                     if constexpr (CH == 32) tmem_ld_x32(taddr + c, v);
                     else tmem_ld_x16(taddr + c, v);
                     tmem_ld_wait();
-                    if (p < rowsP) {
-#pragma unroll
-                        for (int j = 0; j < CH; j += 4) {
-                            const int q = q0 + c + j;
-                            int4 o;
-                            o.x = (int32_t)v[j] >> 8;
-                            o.y = (int32_t)v[j + 1] >> 8;
-                            o.z = (int32_t)v[j + 2] >> 8;
-                            o.w = (int32_t)v[j + 3] >> 8;
-                            if (vec_ok && q + 3 < rowsQ) {
-                                *reinterpret_cast<int4 *>(crow + c + j) = o;
-                            } else {
-                                if (q < rowsQ) crow[c + j] = o.x;
-                                if (q + 1 < rowsQ) crow[c + j + 1] = o.y;
-                                if (q + 2 < rowsQ) crow[c + j + 2] = o.z;
-                                if (q + 3 < rowsQ) crow[c + j + 3] = o.w;
-                            }
-                        }
-                    }
+                    store_block_rows<CH>(v, stage, lane, C, ldc, row0, q0 + c, rowsP, rowsQ, vec_ok);
                 }
             } else {
                 // C[q0 + j][p]: lanes hold consecutive p, so each column is one coalesced 128-byte store.

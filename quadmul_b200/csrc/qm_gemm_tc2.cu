@@ -3,30 +3,56 @@
 //
 // Same contract as gemm_tc_kernel (exact int32 C = A * B^T on nibbles; replaces the reference's
 // igemm<Config>, kernel.cu:62-266).  The difference is where the converted A lives.  The pair tile of
-// gemm_tc_kernel is bound by the shared-memory data pipe: per 128-element K block each SM moves 16 KB
+// gemm_tc_kernel is bound by the shared-memory data pipe: per 128 elements of K each SM moves 16 KB
 // of TMA writes, 16 KB of converter loads, 32 KB of converter stores and 32 KB of MMA operand reads.
 // Here the four A-converter warps keep their 128 rows in registers after the s4 -> s8 split and write
 // them to TMEM with tcgen05.st; tcgen05.mma takes A as [tmem] and only B as a shared-memory
-// descriptor.  That removes A's 16 KB of stores and 16 KB of MMA reads per K block.
+// descriptor.  That removes A's 16 KB of stores and 16 KB of MMA reads per 128 elements of K.
+//
+// A pipeline stage holds H sub-blocks of 128 K-elements (H = 2: 256 elements, 8 MMAs per stage), so the
+// barrier hand-offs and tcgen05.commit are paid once per 2 x 512 tensor-clocks.
 //
 // TMEM map (512 columns): [0, 256) one int32 accumulator (128 lanes x 256 columns per CTA);
-// [256, 256 + 32*S) a ring of S converted A stages, 128 lanes x 32 columns each (128 bytes of K per
-// row: four 32-byte MMA slices, each = 16 bytes of even elements then 16 bytes of odd elements, the
-// same K order the B converters produce).  With one accumulator the epilogue does not overlap the
-// next tile's MMAs; the loaders and converters do run ahead during it.
+// [256, 256 + 32*H*S) a ring of S converted A stages, 128 lanes x 32 columns per sub-block (128 bytes
+// of K per row: four 32-byte MMA slices, each = 16 bytes of even elements then 16 bytes of odd
+// elements, the same K order the B converters produce).  With one accumulator the epilogue does not
+// overlap the next tile's MMAs; the loaders and converters do run ahead during it.
 //
 // Warps: 0 TMA producer, 1 MMA issuer (leader CTA only) and TMEM owner, 2-5 epilogue, 6-9 A
 // converters (warp & 3 = TMEM lane quarter = 32-row block), 10-17 B converters.
-// Packed A tiles are loaded with the 64-byte TMA swizzle so that one thread can read its whole
-// 64-byte row as four conflict-free 16-byte loads; packed B tiles are linear as in gemm_tc_kernel.
+// Packed A sub-blocks are loaded with the 64-byte TMA swizzle so that one thread can read its whole
+// 64-byte row as four conflict-free 16-byte loads; packed B sub-blocks are linear as in gemm_tc_kernel.
 // All waits are bounded as in gemm_tc_kernel.
 #include <cuda.h>
 
 #include <cstdio>
 #include <cstdlib>
 
+#include "qm_epilogue.cuh"
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
+
+// Optional per-role cycle accounting (compiled in only with -DQM_TC2_PROFILE): each role adds the
+// cycles between consecutive PROF marks to a slot; block 0 dumps them to g_tc2_prof at exit.
+#ifdef QM_TC2_PROFILE
+__device__ long long g_tc2_prof[128];
+#define PROF_DECL         \
+    long long pt_[8] = {}; \
+    long long pt0_ = clock64();
+#define PROF(i)                 \
+    {                           \
+        long long n_ = clock64(); \
+        pt_[i] += n_ - pt0_;     \
+        pt0_ = n_;               \
+    }
+#define PROF_DUMP(role)                                                    \
+    if (blockIdx.x < 2 && lane == 0)                                       \
+        for (int i_ = 0; i_ < 8; ++i_) g_tc2_prof[(blockIdx.x * 8 + (role)) * 8 + i_] = pt_[i_];
+#else
+#define PROF_DECL
+#define PROF(i)
+#define PROF_DUMP(role)
+#endif
 
 namespace qm {
 
@@ -34,33 +60,44 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBN = 256;            // UMMA N of the pair tile
-constexpr int kRowsA = 128;         // A rows per CTA
-constexpr int kRowsB = kBN / 2;     // B rows per CTA
-constexpr int kKBlock = 128;
-constexpr int kPkRowBytes = 64;
+constexpr int kBN = 256;         // UMMA N of the pair tile
+constexpr int kRowsA = 128;      // A rows per CTA
+constexpr int kRowsB = kBN / 2;  // B rows per CTA
+constexpr int kSubK = 128;       // K elements per sub-block
+constexpr int kPkRowBytes = 64;  // packed bytes per row per sub-block
 constexpr int kCvRowBytes = 128;
-constexpr int kS = 6;               // converted stages: B in shared memory, A in TMEM
-constexpr int kSP = 6;              // packed stages
-constexpr int kPkStage = (kRowsA + kRowsB) * kPkRowBytes;  // 16 KB
-constexpr int kCvStage = kRowsB * kCvRowBytes;             // 16 KB
+constexpr int kPkSubA = kRowsA * kPkRowBytes;  // 8 KB
+constexpr int kPkSubB = kRowsB * kPkRowBytes;  // 8 KB
+constexpr int kCvSub = kRowsB * kCvRowBytes;   // 16 KB
+constexpr int kASubCols = 32;
 constexpr int kAccCols = kBN;
-constexpr int kAStageCols = 32;
 constexpr int kTmemCols = 512;
 constexpr int kNumAConvWarps = 4, kNumBConvWarps = 8;
 constexpr int kFirstAConvWarp = 6, kFirstBConvWarp = 10;
 constexpr int kNumWarps = kFirstBConvWarp + kNumBConvWarps;  // 18
 constexpr int kNumThreads = kNumWarps * 32;
 constexpr int kBConvThreads = kNumBConvWarps * 32;
-constexpr int kBItems = kRowsB * 4;
-constexpr int kBItemIters = kBItems / kBConvThreads;  // 2
-constexpr int kNumBarriers = 2 * kSP + 2 * kS + 2;
-constexpr int kSmemBytes = 1024 + kS * kCvStage + kSP * kPkStage + kNumBarriers * 8 + 16;
+constexpr int kBItemsSub = kRowsB * 4;                      // 16-byte packed chunks per sub-block
+constexpr int kBItersSub = kBItemsSub / kBConvThreads;      // 2
+constexpr int kArrivals = kNumAConvWarps + kNumBConvWarps;  // converter warps per CTA
+constexpr int kEpiBytes = 4 * 2 * kTmaStoreBufBytes;  // two 4 KB store buffers per epilogue warp (also hold the fallback transposer)
+static_assert(2 * kTmaStoreBufBytes >= EpilogueStage<32>::kBytesPerWarp, "fallback transposer fits");
 constexpr int kRasterGroup = 8;
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
-static_assert(kAccCols + kS * kAStageCols <= kTmemCols, "TMEM budget");
-static_assert(kBItems % kBConvThreads == 0, "B items");
-static_assert(kSmemBytes <= 232448, "shared memory");
+static_assert(kBItemsSub % kBConvThreads == 0, "B items");
+
+template <int H>
+struct Tc2Cfg {
+    static constexpr int S = 6 / H;   // converted stages: B in shared memory, A in TMEM
+    static constexpr int SP = 6 / H;  // packed stages
+    static constexpr int kPkStage = H * (kPkSubA + kPkSubB);
+    static constexpr int kCvStage = H * kCvSub;
+    static constexpr int kAStageCols = H * kASubCols;
+    static constexpr int kNumBarriers = 2 * SP + 2 * S + 2;
+    static constexpr int kSmemBytes = 1024 + S * kCvStage + SP * kPkStage + kEpiBytes + kNumBarriers * 8 + 16;
+    static_assert(kAccCols + S * kAStageCols <= kTmemCols, "TMEM budget");
+    static_assert(kSmemBytes <= 232448, "shared memory");
+};
 
 __device__ __forceinline__ void tile_coords2(int t, int tilesP, int tilesQ, int &tp, int &tq)
 {
@@ -97,6 +134,15 @@ __device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uin
         : "memory");
 }
 
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair once every MMA
+// issued so far has finished (a barrier signal, not a data transfer).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&v)[32])
 {
     asm volatile(
@@ -115,22 +161,27 @@ __device__ __forceinline__ void tmem_st_wait()
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+template <int H, bool MC>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-                int32_t *__restrict__ C, int64_t ldc, int M, int N, int K, int *status)
+                const __grid_constant__ CUtensorMap tmapC, int use_tma_store, int32_t *__restrict__ C, int64_t ldc, int M,
+                int N, int K, int *status)
 {
+    using Cfg = Tc2Cfg<H>;
+    constexpr int S = Cfg::S, SP = Cfg::SP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_u32 = smem_u32(smem_raw);
-    const uint32_t cv0 = (raw_u32 + 1023u) & ~1023u;  // converted B stages
-    const uint32_t pk0 = cv0 + kS * kCvStage;         // packed stages: A (swizzle 64B) then B (linear)
-    const uint32_t bar0 = pk0 + kSP * kPkStage;
+    const uint32_t cv0 = (raw_u32 + 1023u) & ~1023u;   // converted B stages: [stage][sub-block][row][128 B]
+    const uint32_t pk0 = cv0 + S * Cfg::kCvStage;      // packed stages: [stage][A sub-blocks (swizzle 64B)][B sub-blocks (linear)]
+    const uint32_t epi0 = pk0 + SP * Cfg::kPkStage;    // epilogue transpose buffers
+    const uint32_t bar0 = epi0 + kEpiBytes;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
-    auto pk_empty = [&](int s) { return bar0 + 8u * (kSP + s); };
-    auto cv_full = [&](int s) { return bar0 + 8u * (2 * kSP + s); };        // leader's copy is the one waited on
-    auto cv_empty = [&](int s) { return bar0 + 8u * (2 * kSP + kS + s); };  // one per CTA
-    const uint32_t acc_full = bar0 + 8u * (2 * kSP + 2 * kS);
+    auto pk_empty = [&](int s) { return bar0 + 8u * (SP + s); };
+    auto cv_full = [&](int s) { return bar0 + 8u * (2 * SP + s); };       // leader's copy is the one waited on
+    auto cv_empty = [&](int s) { return bar0 + 8u * (2 * SP + S + s); };  // one per CTA
+    const uint32_t acc_full = bar0 + 8u * (2 * SP + 2 * S);
     const uint32_t acc_empty = acc_full + 8u;
-    const uint32_t tmem_slot = bar0 + 8u * kNumBarriers;
+    const uint32_t tmem_slot = bar0 + 8u * Cfg::kNumBarriers;
     uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(smem_raw + (tmem_slot - raw_u32));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_raw + (tmem_slot + 4 - raw_u32));
 
@@ -139,15 +190,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     const int unit = (int)(blockIdx.x >> 1), num_units = (int)(gridDim.x >> 1);
     const int tilesP = (M + 255) / 256, tilesQ = (N + kBN - 1) / kBN;
     const int num_tiles = tilesP * tilesQ;
-    const int num_kb = (K + kKBlock - 1) / kKBlock;
+    const int num_kb = (K + H * kSubK - 1) / (H * kSubK);  // stages per tile; TMA zero-fills beyond K
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kSP; ++s) {
+        for (int s = 0; s < SP; ++s) {
             mbar_init(pk_full(s), 1);
-            mbar_init(pk_empty(s), kNumAConvWarps + kNumBConvWarps);
+            mbar_init(pk_empty(s), kArrivals);
         }
-        for (int s = 0; s < kS; ++s) {
-            mbar_init(cv_full(s), 2 * (kNumAConvWarps + kNumBConvWarps));
+        for (int s = 0; s < S; ++s) {
+            mbar_init(cv_full(s), 2 * kArrivals);
             mbar_init(cv_empty(s), 1);
         }
         mbar_init(acc_full, 1);
@@ -159,6 +210,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     if (warp == 0 && lane == 0) {
         prefetch_tmap(&tmapA);
         prefetch_tmap(&tmapB);
+        if (use_tma_store) prefetch_tmap(&tmapC);
     }
     if (warp == 1) {
         tmem_alloc<2>(tmem_slot, kTmemCols);
@@ -177,26 +229,34 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
                 tile_coords2(t, tilesP, tilesQ, tp, tq);
                 const int yA = tp * 256 + (int)cta_rank * kRowsA;
                 const int yB = tq * kBN + (int)cta_rank * kRowsB;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kSP;
-                    const uint32_t ph = (it / kSP) & 1u;
+                    const int s = it % SP;
+                    const uint32_t ph = (it / SP) & 1u;
                     if (!mbar_wait(pk_empty(s), ph ^ 1u, abort_flag)) {
                         report_timeout2(status, kWaitProducerSlot);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    const uint32_t dst = pk0 + s * kPkStage;
-                    mbar_arrive_expect_tx(pk_full(s), kPkStage);
-                    tma_load_2d(dst, &tmapA, kb * kPkRowBytes, yA, pk_full(s));
-                    tma_load_2d(dst + kRowsA * kPkRowBytes, &tmapB, kb * kPkRowBytes, yB, pk_full(s));
+                    PROF(0)
+                    const uint32_t dst = pk0 + s * Cfg::kPkStage;
+                    mbar_arrive_expect_tx(pk_full(s), Cfg::kPkStage);
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+                        const int x = (kb * H + h) * kPkRowBytes;
+                        tma_load_2d(dst + h * kPkSubA, &tmapA, x, yA, pk_full(s));
+                        tma_load_2d(dst + H * kPkSubA + h * kPkSubB, &tmapB, x, yB, pk_full(s));
+                    }
+                    PROF(1)
                 }
             }
+            PROF_DUMP(0)
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -204,36 +264,53 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         if (lane == 0 && cta_rank == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
+            PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units, ++lt) {
+                PROF(3)
                 if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag)) {
                     report_timeout2(status, kWaitMmaAcc);
                     *abort_flag = 1;
                     break;
                 }
+                PROF(0)
                 tc_fence_after_sync();
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kS;
-                    const uint32_t ph = (it / kS) & 1u;
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
                     if (!mbar_wait(cv_full(s), ph, abort_flag)) {
                         report_timeout2(status, kWaitMmaOperands);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
+                    PROF(1)
                     tc_fence_after_sync();
-                    const uint64_t dB = make_smem_desc2(cv0 + s * kCvStage);
-                    const uint32_t ta = tmem_a0 + (uint32_t)(s * kAStageCols);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        umma_i8_ta(tmem_base, ta + 8u * k4, dB + 2u * k4, kIdesc, (kb | k4) != 0 ? 1u : 0u);
-                    umma_commit<2>(cv_empty(s));
-                    umma_commit<2>(mapa_cluster(cv_empty(s), 1));
+                    for (int h = 0; h < H; ++h) {
+                        const uint64_t dB = make_smem_desc2(cv0 + s * Cfg::kCvStage + h * kCvSub);
+                        const uint32_t ta = tmem_a0 + (uint32_t)(s * Cfg::kAStageCols + h * kASubCols);
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4)
+                            umma_i8_ta(tmem_base, ta + 8u * k4, dB + 2u * k4, kIdesc, (kb | h | k4) != 0 ? 1u : 0u);
+                    }
+                    if constexpr (MC) {
+                        umma_commit_pair(cv_empty(s));
+                    } else {
+                        umma_commit<2>(cv_empty(s));
+                        umma_commit<2>(mapa_cluster(cv_empty(s), 1));
+                    }
+                    PROF(2)
                 }
                 if (ok) {
-                    umma_commit<2>(acc_full);
-                    umma_commit<2>(mapa_cluster(acc_full, 1));
+                    if constexpr (MC) {
+                        umma_commit_pair(acc_full);
+                    } else {
+                        umma_commit<2>(acc_full);
+                        umma_commit<2>(mapa_cluster(acc_full, 1));
+                    }
                 }
             }
+            PROF_DUMP(1)
         }
         __syncwarp();
     } else if (warp < kFirstAConvWarp) {
@@ -241,10 +318,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         const int quarter = warp & 3;
         uint32_t lt = 0;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && ((ldc & 3) == 0);
+        PROF_DECL
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
             tile_coords2(t, tilesP, tilesQ, tp, tq);
+            PROF(2)
             const bool ok = warp_wait<false>(acc_full, lt & 1u, abort_flag, lane);
+            PROF(0)
             if (!ok) {
                 if (lane == 0) {
                     report_timeout2(status, kWaitEpilogueAcc);
@@ -254,49 +334,54 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             }
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const int p = tp * 256 + (int)cta_rank * kRowsA + quarter * 32 + lane;
+            const int row0 = tp * 256 + (int)cta_rank * kRowsA + quarter * 32;
             const int q0 = tq * kBN;
-            int32_t *crow = C + (int64_t)p * ldc + q0;
+            const uint32_t stage = epi0 + (uint32_t)((warp - 2) * 2 * kTmaStoreBufBytes);
+            // two TMEM loads in flight: the next block is fetched while this one is stored
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(taddr, va);
+            if (use_tma_store) {
 #pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                uint32_t v[32];
-                tmem_ld_x32(taddr + c, v);
-                tmem_ld_wait();
-                if (p < M) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int q = q0 + c + j;
-                        int4 o;
-                        o.x = (int32_t)v[j] >> 8;
-                        o.y = (int32_t)v[j + 1] >> 8;
-                        o.z = (int32_t)v[j + 2] >> 8;
-                        o.w = (int32_t)v[j + 3] >> 8;
-                        if (vec_ok && q + 3 < N) {
-                            *reinterpret_cast<int4 *>(crow + c + j) = o;
-                        } else {
-                            if (q < N) crow[c + j] = o.x;
-                            if (q + 1 < N) crow[c + j + 1] = o.y;
-                            if (q + 2 < N) crow[c + j + 2] = o.z;
-                            if (q + 3 < N) crow[c + j + 3] = o.w;
-                        }
-                    }
+                for (int c = 0; c < kBN; c += 64) {
+                    tmem_ld_wait();
+                    tmem_ld_x32(taddr + c + 32, vb);
+                    store_block_tma(va, stage, lane, &tmapC, q0 + c, row0, lt > 0 || c > 0);
+                    tmem_ld_wait();
+                    if (c + 64 < kBN) tmem_ld_x32(taddr + c + 64, va);
+                    store_block_tma(vb, stage + kTmaStoreBufBytes, lane, &tmapC, q0 + c + 32, row0, lt > 0 || c > 0);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 64) {
+                    tmem_ld_wait();
+                    tmem_ld_x32(taddr + c + 32, vb);
+                    store_block_rows<32>(va, stage, lane, C, ldc, row0, q0 + c, M, N, vec_ok);
+                    tmem_ld_wait();
+                    if (c + 64 < kBN) tmem_ld_x32(taddr + c + 64, va);
+                    store_block_rows<32>(vb, stage, lane, C, ldc, row0, q0 + c + 32, M, N, vec_ok);
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+            PROF(1)
         }
+        if (use_tma_store && lane == 0) tma_store_wait_all();  // the buffers must outlive the stores that read them
+        __syncwarp();
+        if (warp == 2) { PROF_DUMP(2) }
     } else if (warp < kFirstBConvWarp) {
         // ------------------------------ A converters: packed smem -> registers -> TMEM ------------------------------
         const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;           // row of this CTA's A tile = TMEM lane
+        const int r = quarter * 32 + lane;              // row of this CTA's A tile = TMEM lane
         const uint32_t swz = (uint32_t)((r >> 1) & 3);  // 64-byte TMA swizzle: chunk ^= (row / 2) % 4
         uint32_t it = 0;
         bool ok = true;
+        PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int ps = it % kSP, cs = it % kS;
-                const uint32_t pph = (it / kSP) & 1u, cph = (it / kS) & 1u;
+                const int ps = it % SP, cs = it % S;
+                const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
+                PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout2(status, kWaitConvertPacked);
@@ -305,24 +390,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                const uint32_t src = pk0 + ps * kPkStage + (uint32_t)r * kPkRowBytes;
-                uint4 w[4];
+                PROF(0)
+                const uint32_t src = pk0 + ps * Cfg::kPkStage + (uint32_t)r * kPkRowBytes;
+                uint4 w[H][4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) w[c] = lds128(src + (((uint32_t)c ^ swz) << 4));
-                uint32_t v[32];
+                for (int h = 0; h < H; ++h)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    v[8 * c + 0] = (w[c].x << 4) & 0xF0F0F0F0u;
-                    v[8 * c + 1] = (w[c].y << 4) & 0xF0F0F0F0u;
-                    v[8 * c + 2] = (w[c].z << 4) & 0xF0F0F0F0u;
-                    v[8 * c + 3] = (w[c].w << 4) & 0xF0F0F0F0u;
-                    v[8 * c + 4] = w[c].x & 0xF0F0F0F0u;
-                    v[8 * c + 5] = w[c].y & 0xF0F0F0F0u;
-                    v[8 * c + 6] = w[c].z & 0xF0F0F0F0u;
-                    v[8 * c + 7] = w[c].w & 0xF0F0F0F0u;
-                }
+                    for (int c = 0; c < 4; ++c) w[h][c] = lds128(src + h * kPkSubA + (((uint32_t)c ^ swz) << 4));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));  // packed rows are in registers now
+                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout2(status, kWaitConvertSlot);
@@ -331,23 +408,44 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
+                PROF(2)
                 tc_fence_after_sync();
-                tmem_st_x32(tmem_a0 + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cs * kAStageCols), v);
+                const uint32_t ta = tmem_a0 + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cs * Cfg::kAStageCols);
+#pragma unroll
+                for (int h = 0; h < H; ++h) {
+                    uint32_t v[32];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        v[8 * c + 0] = (w[h][c].x << 4) & 0xF0F0F0F0u;
+                        v[8 * c + 1] = (w[h][c].y << 4) & 0xF0F0F0F0u;
+                        v[8 * c + 2] = (w[h][c].z << 4) & 0xF0F0F0F0u;
+                        v[8 * c + 3] = (w[h][c].w << 4) & 0xF0F0F0F0u;
+                        v[8 * c + 4] = w[h][c].x & 0xF0F0F0F0u;
+                        v[8 * c + 5] = w[h][c].y & 0xF0F0F0F0u;
+                        v[8 * c + 6] = w[h][c].z & 0xF0F0F0F0u;
+                        v[8 * c + 7] = w[h][c].w & 0xF0F0F0F0u;
+                    }
+                    tmem_st_x32(ta + h * kASubCols, v);
+                }
                 tmem_st_wait();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(cv_full(cs), 0);
+                PROF(3)
             }
         }
+        if (warp == kFirstAConvWarp) { PROF_DUMP(3) }
     } else {
         // ------------------------------ B converters: packed smem -> swizzled int8 smem ------------------------------
         const int ctid = threadIdx.x - kFirstBConvWarp * 32;
         uint32_t it = 0;
         bool ok = true;
+        PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int ps = it % kSP, cs = it % kS;
-                const uint32_t pph = (it / kSP) & 1u, cph = (it / kS) & 1u;
+                const int ps = it % SP, cs = it % S;
+                const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
+                PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout2(status, kWaitConvertPacked);
@@ -356,12 +454,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                const uint32_t src = pk0 + ps * kPkStage + kRowsA * kPkRowBytes;
-                uint4 w[kBItemIters];
+                PROF(0)
+                const uint32_t src = pk0 + ps * Cfg::kPkStage + H * kPkSubA;
+                uint4 w[H][kBItersSub];
 #pragma unroll
-                for (int j = 0; j < kBItemIters; ++j) w[j] = lds128(src + (j * kBConvThreads + ctid) * 16);
+                for (int h = 0; h < H; ++h)
+#pragma unroll
+                    for (int j = 0; j < kBItersSub; ++j) w[h][j] = lds128(src + h * kPkSubB + (j * kBConvThreads + ctid) * 16);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));
+                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout2(status, kWaitConvertSlot);
@@ -370,30 +472,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
+                PROF(2)
                 tc_fence_after_sync();
-                const uint32_t dst = cv0 + cs * kCvStage;
+                const uint32_t dst = cv0 + cs * Cfg::kCvStage;
 #pragma unroll
-                for (int j = 0; j < kBItemIters; ++j) {
-                    const int i = j * kBConvThreads + ctid;
-                    const int rr = i >> 2, c = i & 3;
-                    const uint32_t d = dst + rr * kCvRowBytes + (((2 * c) ^ (rr & 7)) << 4);
-                    uint4 lo, hi;
-                    lo.x = (w[j].x << 4) & 0xF0F0F0F0u;
-                    lo.y = (w[j].y << 4) & 0xF0F0F0F0u;
-                    lo.z = (w[j].z << 4) & 0xF0F0F0F0u;
-                    lo.w = (w[j].w << 4) & 0xF0F0F0F0u;
-                    hi.x = w[j].x & 0xF0F0F0F0u;
-                    hi.y = w[j].y & 0xF0F0F0F0u;
-                    hi.z = w[j].z & 0xF0F0F0F0u;
-                    hi.w = w[j].w & 0xF0F0F0F0u;
-                    sts128(d, lo);
-                    sts128(d ^ 16u, hi);
-                }
+                for (int h = 0; h < H; ++h)
+#pragma unroll
+                    for (int j = 0; j < kBItersSub; ++j) {
+                        const int i = j * kBConvThreads + ctid;
+                        const int rr = i >> 2, c = i & 3;
+                        const uint32_t d = dst + h * kCvSub + rr * kCvRowBytes + (((2 * c) ^ (rr & 7)) << 4);
+                        uint4 lo, hi;
+                        lo.x = (w[h][j].x << 4) & 0xF0F0F0F0u;
+                        lo.y = (w[h][j].y << 4) & 0xF0F0F0F0u;
+                        lo.z = (w[h][j].z << 4) & 0xF0F0F0F0u;
+                        lo.w = (w[h][j].w << 4) & 0xF0F0F0F0u;
+                        hi.x = w[h][j].x & 0xF0F0F0F0u;
+                        hi.y = w[h][j].y & 0xF0F0F0F0u;
+                        hi.z = w[h][j].z & 0xF0F0F0F0u;
+                        hi.w = w[h][j].w & 0xF0F0F0F0u;
+                        sts128(d, lo);
+                        sts128(d ^ 16u, hi);
+                    }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(cv_full(cs), 0);
+                PROF(3)
             }
         }
+        if (warp == kFirstBConvWarp) { PROF_DUMP(4) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -439,16 +546,26 @@ int make_tmap2(CUtensorMap *map, const void *base, int rows, int64_t kbytes, int
     return QM_OK;
 }
 
-}  // namespace
-
-int tc2_prepare_device()
+// C as a 2-D int32 tensor [M][N] with row pitch ldc; 32 x 32 boxes, 128-byte swizzle.
+int make_tmap_c(CUtensorMap *map, const int32_t *C, int m, int n, int64_t ldc)
 {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    return e == cudaSuccess ? QM_OK : record_cuda_error(e, "cudaFuncSetAttribute(shared memory)");
+    EncodeTiledFn2 fn = encode_fn2();
+    if (!fn) return record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point");
+    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(C), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(C)");
+    return QM_OK;
 }
 
-int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
+template <int H, bool MC>
+int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
 {
+    auto kernel = gemm_tc2_kernel<H, MC>;
     const int64_t kbytes = g.k / 2;
     CUtensorMap tmA, tmB;
     int st = make_tmap2(&tmA, g.A, g.m, kbytes, kRowsA, CU_TENSOR_MAP_SWIZZLE_64B);
@@ -457,10 +574,19 @@ int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
     if (st != QM_OK) return st;
     const int64_t tiles = (int64_t)((g.m + 255) / 256) * ((g.n + kBN - 1) / kBN);
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
+    // TMA store of C needs a 16-byte-aligned base and row pitch; otherwise the kernel stores with plain vectors
+    static const bool allow_tma_store = !std::getenv("QM_NO_TMA_STORE");
+    const int use_tma_store =
+        (allow_tma_store && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && g.ldc < (1ll << 36)) ? 1 : 0;
+    CUtensorMap tmC = tmA;  // placeholder when unused
+    if (use_tma_store) {
+        st = make_tmap_c(&tmC, g.C, g.m, g.n, g.ldc);
+        if (st != QM_OK) return st;
+    }
 
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kNumThreads, 1, 1);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.dynamicSmemBytes = Tc2Cfg<H>::kSmemBytes;
     cfg.stream = g.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -475,7 +601,7 @@ int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
     if (cached == 0) {
         cfg.gridDim = dim3((unsigned)(2 * (ctx.num_sms / 2)), 1, 1);
         int n = 0;
-        cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel, &cfg);
+        cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
         if (qe != cudaSuccess) return record_cuda_error(qe, "cudaOccupancyMaxActiveClusters");
         cached = n > 0 ? n : 1;
     }
@@ -484,9 +610,48 @@ int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
     if (units < 1) units = 1;
     if (tiles < units) units = (int)tiles;
     cfg.gridDim = dim3((unsigned)(units * 2), 1, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, tmA, tmB, g.C, g.ldc, g.m, g.n, g.k, ctx.status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc2_kernel launch");
     return QM_OK;
 }
+
+}  // namespace
+
+#define QM_TC2_FOR_EACH(X) X(1, false) X(2, false) X(1, true) X(2, true)
+
+int tc2_prepare_device()
+{
+    cudaError_t e;
+#define X(H, MC)                                                                                                          \
+    e = cudaFuncSetAttribute(gemm_tc2_kernel<H, MC>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Cfg<H>::kSmemBytes); \
+    if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(shared memory)");
+    QM_TC2_FOR_EACH(X)
+#undef X
+    return QM_OK;
+}
+
+// Variant: sub-blocks per stage (1 or 2) and one pair-wide commit (1) or two single commits (0).
+// Measured at 8192^3 on B200: "10" 442 us, "11" 418 us, "20" 337 us, "21" 328 us (before the TMA-store
+// epilogue; 303 us with it), so "21" is the default.  The environment variable QM_TC2_VARIANT overrides it.
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    static const int variant = []() {
+        const char *e = std::getenv("QM_TC2_VARIANT");
+        return (e && (e[0] == '1' || e[0] == '2') && (e[1] == '0' || e[1] == '1')) ? (e[0] - '0') * 10 + (e[1] - '0') : 21;
+    }();
+#define X(H, MC) \
+    if (variant == H * 10 + (MC ? 1 : 0)) return tc2_launch_variant<H, MC>(g, ctx);
+    QM_TC2_FOR_EACH(X)
+#undef X
+    return QM_ERR_ARG;
+}
+
+#ifdef QM_TC2_PROFILE
+extern "C" int qm_debug_tc2_profile(long long *out64)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out64, g_tc2_prof, sizeof(long long) * 128);
+    return e == cudaSuccess ? 0 : 4;
+}
+#endif
 
 }  // namespace qm

@@ -61,6 +61,9 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
         else if (n <= 64) p.tile_n = 64;
         else if (n <= 128) p.tile_n = 128;
         if (p.cta_pair == 2 && p.tile_n < 128) p.cta_pair = 1;
+        // the 256 x 256 pair tile takes operand A through TMEM (gemm_tc2_kernel): 3.5 POPS against 2.3 POPS
+        // for the all-shared-memory pair tile at 8192^3
+        if (p.cta_pair == 2 && p.tile_n == 256) p.a_tmem = 1;
     }
     return p;
 }
