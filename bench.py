@@ -38,9 +38,9 @@ METRIC = "int4 GEMM TOPS at M=N=K=8192"
 UNIT = "TOPS"
 INT8_PEAK_NOMINAL_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
 FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of gemm_tc_kernel, from the ncu
-# capture summarised in profiles/gemm_tc_8192.md (None until that capture exists)
-DRAM_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of gemm_tc2_kernel (164.6 MB + 222.1 MB),
+# from the ncu capture summarised in profiles/gemm_tc2_8192.md
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = 386.7e6
 
 
 def config(n_gpus: int) -> dict:

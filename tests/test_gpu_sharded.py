@@ -1,0 +1,98 @@
+"""Column-sharded GEMM on real devices.
+
+On one GPU the ranks are emulated one after another on the same device (each rank's slab written through
+qm_gemm_s4_ldc into the full-width C, and the gather path through qm_unshard_c).  With two or more GPUs
+the same check runs as one process per GPU over NCCL, including the optional all-gather of C."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from _util import to_dev
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("world,m,n,k", [(2, 300, 1024, 512), (4, 64, 11008, 256), (8, 260, 2048, 384), (3, 16, 1000, 128)])
+def test_shards_emulated_on_one_gpu(qm, cuda_clean, oracle, world, m, n, k):
+    torch = cuda_clean
+    from quadmul_b200.sharded import NShardedGemm
+
+    ap = oracle.fill_packed(m, k, 21); bp = oracle.fill_packed(n, k, 22)
+    want = oracle.gemm(ap, bp)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    full = torch.full((m, n), -9, dtype=torch.int32, device="cuda")
+    shards = [NShardedGemm(n, world=world, rank=r) for r in range(world)]
+    stride = shards[0].slab_stride
+    slabs = torch.zeros((world, m, stride), dtype=torch.int32, device="cuda")
+    for sh in shards:
+        # (1) straight into the full-width C through the leading dimension
+        sh.local(a, sh.shard_of(b), m, k, out=full[:, sh.begin : sh.begin + sh.count])
+        # (2) into a padded slab, as a rank would before an all-gather
+        sh.local(a, sh.shard_of(b), m, k, out=slabs[sh.rank])
+    torch.cuda.synchronize()
+    assert np.array_equal(full.cpu().numpy(), want)
+    out = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    qm.unshard_c(slabs, out, m, n, world, stride)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _nccl_worker(rank, world, port, m, n, k, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    import quadmul_b200 as qm
+    from oracle import oracle as o
+    from quadmul_b200.sharded import NShardedGemm
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ap = o.fill_packed(m, k, 5); bp = o.fill_packed(n, k, 6)
+        a = torch.from_numpy(ap).view(torch.int8).cuda()
+        sh = NShardedGemm(n)
+        b = torch.from_numpy(bp[sh.begin : sh.begin + sh.count]).view(torch.int8).cuda()  # a rank holds only its rows of B
+        slab = sh.local(a, b, m, k)
+        full = sh.gather(slab, m)
+        torch.cuda.synchronize()
+        want = o.gemm(ap, bp)
+        ok = bool(np.array_equal(full.cpu().numpy(), want))
+        code, _ = qm.device_status()
+        q.put((rank, ok and code == 0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_shards_over_nccl(qm, cuda_clean):
+    torch = cuda_clean
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, 520, 4096 + 128, 1024, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in results), results
