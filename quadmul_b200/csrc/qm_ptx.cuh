@@ -9,7 +9,7 @@ namespace qm {
 namespace ptx {
 
 #ifndef QM_WAIT_LIMIT_NS
-#define QM_WAIT_LIMIT_NS 1000000000ull  // 1 s per wait, far beyond any legitimate stall
+#define QM_WAIT_LIMIT_NS 200000000ull  // 0.2 s per wait, far beyond any legitimate stall (whole kernels take < 30 ms)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)

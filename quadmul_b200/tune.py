@@ -82,6 +82,8 @@ def main():
                 if exc.status in (7, 8):  # variant not built, or scratch too small for this split
                     continue
                 raise
+            if code != 0:
+                raise SystemExit(f"tune: in-kernel wait expired for {m}x{n}x{k} {opts}; stopping")
             rows.append((ms, opts))
             print(json.dumps({"m": m, "n": n, "k": k, **opts, "us": round(ms * 1e3, 2), "tops": round(ops / ms / 1e9, 1),
                               "gbs": round(nbytes / ms / 1e6, 1), "status": code}), flush=True)
