@@ -18,8 +18,8 @@
 // elements, the same K order the B converters produce).  With one accumulator the epilogue does not
 // overlap the next tile's MMAs; the loaders and converters do run ahead during it.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (leader CTA only) and TMEM owner, 2-5 epilogue, 6-9 A
-// converters (warp & 3 = TMEM lane quarter = 32-row block), 10-17 B converters.
+// Warps: 0 TMA producer, 1 MMA issuer (leader CTA only) and TMEM owner, 2-9 epilogue (two per TMEM lane
+// quarter), 10-13 A converters (warp & 3 = TMEM lane quarter = 32-row block), 14-21 B converters.
 // Packed A sub-blocks are loaded with the 64-byte TMA swizzle so that one thread can read its whole
 // 64-byte row as four conflict-free 16-byte loads; packed B sub-blocks are linear as in gemm_tc_kernel.
 // All waits are bounded as in gemm_tc_kernel.
@@ -72,16 +72,18 @@ constexpr int kCvSub = kRowsB * kCvRowBytes;   // 16 KB
 constexpr int kASubCols = 32;
 constexpr int kAccCols = kBN;
 constexpr int kTmemCols = 512;
+constexpr int kNumEpiWarps = 8;  // two per TMEM lane quarter, 128 accumulator columns each
 constexpr int kNumAConvWarps = 4, kNumBConvWarps = 8;
-constexpr int kFirstAConvWarp = 6, kFirstBConvWarp = 10;
-constexpr int kNumWarps = kFirstBConvWarp + kNumBConvWarps;  // 18
+constexpr int kFirstAConvWarp = 2 + kNumEpiWarps, kFirstBConvWarp = kFirstAConvWarp + kNumAConvWarps;
+constexpr int kNumWarps = kFirstBConvWarp + kNumBConvWarps;  // 22
 constexpr int kNumThreads = kNumWarps * 32;
 constexpr int kBConvThreads = kNumBConvWarps * 32;
 constexpr int kBItemsSub = kRowsB * 4;                      // 16-byte packed chunks per sub-block
 constexpr int kBItersSub = kBItemsSub / kBConvThreads;      // 2
 constexpr int kArrivals = kNumAConvWarps + kNumBConvWarps;  // converter warps per CTA
-constexpr int kEpiBytes = 4 * 2 * kTmaStoreBufBytes;  // two 4 KB store buffers per epilogue warp (also hold the fallback transposer)
-static_assert(2 * kTmaStoreBufBytes >= EpilogueStage<32>::kBytesPerWarp, "fallback transposer fits");
+constexpr int kEpiBufBytes = kTmaStoreBufBytes;  // per epilogue warp: one 4 KB TMA-store buffer (or the 16-column fallback transposer)
+constexpr int kEpiBytes = kNumEpiWarps * kEpiBufBytes;
+static_assert(kEpiBufBytes >= EpilogueStage<16>::kBytesPerWarp, "epilogue buffer");
 constexpr int kRasterGroup = 8;
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 static_assert(kBItemsSub % kBConvThreads == 0, "B items");
@@ -202,7 +204,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             mbar_init(cv_empty(s), 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 8);
+        mbar_init(acc_empty, 2 * kNumEpiWarps);
         *abort_flag = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -315,9 +317,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         __syncwarp();
     } else if (warp < kFirstAConvWarp) {
         // ------------------------------ epilogue ------------------------------
+        // Warp = (TMEM lane quarter, column half): four 32 x 32 blocks.  Two blocks are held in registers, so the
+        // last TMEM load is issued after only two of the four stores; the accumulator is handed back to the MMA
+        // issuer at that point and the remaining stores run under the next tile's main loop.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         uint32_t lt = 0;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && ((ldc & 3) == 0);
+        const uint32_t buf = epi0 + (uint32_t)((warp - 2) * kEpiBufBytes);
+        bool buf_used = false;
         PROF_DECL
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
@@ -333,40 +341,46 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
             const int row0 = tp * 256 + (int)cta_rank * kRowsA + quarter * 32;
-            const int q0 = tq * kBN;
-            const uint32_t stage = epi0 + (uint32_t)((warp - 2) * 2 * kTmaStoreBufBytes);
-            // two TMEM loads in flight: the next block is fetched while this one is stored
+            const int q0 = tq * kBN + half * 128;
+            auto store = [&](const uint32_t(&v)[32], int col) {
+                if (use_tma_store) {
+                    if (buf_used) {
+                        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the buffer
+                        __syncwarp();
+                    }
+                    store_block_tma(v, buf, lane, &tmapC, col, row0, false);
+                    buf_used = true;
+                } else {
+                    uint32_t h0[16], h1[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        h0[j] = v[j];
+                        h1[j] = v[16 + j];
+                    }
+                    store_block_rows<16>(h0, buf, lane, C, ldc, row0, col, M, N, vec_ok);
+                    store_block_rows<16>(h1, buf, lane, C, ldc, row0, col + 16, M, N, vec_ok);
+                }
+            };
             uint32_t va[32], vb[32];
             tmem_ld_x32(taddr, va);
-            if (use_tma_store) {
-#pragma unroll 1
-                for (int c = 0; c < kBN; c += 64) {
-                    tmem_ld_wait();
-                    tmem_ld_x32(taddr + c + 32, vb);
-                    store_block_tma(va, stage, lane, &tmapC, q0 + c, row0, lt > 0 || c > 0);
-                    tmem_ld_wait();
-                    if (c + 64 < kBN) tmem_ld_x32(taddr + c + 64, va);
-                    store_block_tma(vb, stage + kTmaStoreBufBytes, lane, &tmapC, q0 + c + 32, row0, lt > 0 || c > 0);
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < kBN; c += 64) {
-                    tmem_ld_wait();
-                    tmem_ld_x32(taddr + c + 32, vb);
-                    store_block_rows<32>(va, stage, lane, C, ldc, row0, q0 + c, M, N, vec_ok);
-                    tmem_ld_wait();
-                    if (c + 64 < kBN) tmem_ld_x32(taddr + c + 64, va);
-                    store_block_rows<32>(vb, stage, lane, C, ldc, row0, q0 + c + 32, M, N, vec_ok);
-                }
-            }
+            tmem_ld_x32(taddr + 32, vb);
+            tmem_ld_wait();
+            store(va, q0);
+            tmem_ld_x32(taddr + 64, va);
+            store(vb, q0 + 32);
+            tmem_ld_x32(taddr + 96, vb);
+            tmem_ld_wait();
+            // every column of this warp's share is in registers: the accumulator may be overwritten
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
             PROF(1)
+            store(va, q0 + 64);
+            store(vb, q0 + 96);
         }
-        if (use_tma_store && lane == 0) tma_store_wait_all();  // the buffers must outlive the stores that read them
+        if (use_tma_store && lane == 0) tma_store_wait_all();  // the buffer must outlive the stores that read it
         __syncwarp();
         if (warp == 2) { PROF_DUMP(2) }
     } else if (warp < kFirstBConvWarp) {

@@ -63,7 +63,7 @@ def test_pair_tile_with_a_in_tmem(qm, cuda_clean, oracle, golden):
     for name, g in golden.items():
         got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **opts)
         assert np.array_equal(got, g["c"]), f"{name}: " + mismatch_report(got, g["c"])
-    for m, n, k in [(256, 256, 128), (1024, 1024, 1024), (300, 520, 1056), (2048, 4096, 4096), (257, 8, 32), (513, 1000, 4064)]:
+    for m, n, k in [(256, 256, 128), (1024, 1024, 1024), (300, 520, 1056), (2048, 4096, 4096), (257, 8, 32), (513, 1000, 4064), (300, 519, 256)]:
         ap = oracle.fill_packed(m, k, 61); bp = oracle.fill_packed(n, k, 62)
         _check(qm, cuda_clean, oracle, ap, bp, **opts)
 
