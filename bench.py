@@ -433,6 +433,53 @@ def native_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def byte_kernel_arm(args) -> None:
+    """pack / unpack against the HBM roof: 1.5 bytes of traffic per element."""
+    import torch
+
+    import quadmul_b200 as qm
+    from quadmul_b200 import _lib
+
+    rows, k = (int(x) for x in (args.shape or "16384,16384").split(","))
+    torch.cuda.set_device(0)
+    packed = qm.fill_packed(rows, k, 7)
+    full = qm.unpack(packed)
+    out_p = torch.empty_like(packed)
+    out_u = torch.empty_like(full)
+    stream = torch.cuda.current_stream().cuda_stream
+    if args.op == "pack":
+        fn = lambda: _lib.check(_lib.LIB.qm_pack_s4(full.data_ptr(), out_p.data_ptr(), rows, k, stream), "pack")
+    else:
+        fn = lambda: _lib.check(_lib.LIB.qm_unpack_s4(packed.data_ptr(), out_u.data_ptr(), rows, k, stream), "unpack")
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    avg = ev[0].elapsed_time(ev[-1]) / args.steps
+    nbytes = 1.5 * rows * k
+    peak, note = measured_hbm()
+    ok = torch.equal(out_p, packed) if args.op == "pack" else torch.equal(out_u, full)
+    print(json.dumps({
+        "metric": f"{args.op} GB/s ({rows} x {k} elements)", "value": nbytes / (avg * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": avg, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": f"{args.op} of a {rows} x {k} signed-int4 matrix", "l2": f"{nbytes / 1e6:.0f} MB per launch exceeds the 126 MB L2"},
+        "roofline": {"bound": "hbm", "achieved": nbytes / (avg * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": nbytes / (avg * 1e-3) / 1e9 / peak, "traffic": None, "peak_note": note,
+                     "launch_ms_min": per[0], "launch_ms_median": per[len(per) // 2], "algorithmic_bytes_per_launch": nbytes,
+                     "kernel": f"{args.op}_kernel"},
+        "gpu_launches": args.steps, "clocks": clocks, "round_trip_ok": bool(ok)}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -448,10 +495,15 @@ def main() -> None:
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--a-tmem", type=int, default=0)
     ap.add_argument("--graph", type=int, default=0, help="capture this many launches per step in one CUDA graph")
+    ap.add_argument("--op", choices=["gemm", "pack", "unpack"], default="gemm",
+                    help="pack / unpack: time the HBM-bound byte kernels on a --shape ROWS,K matrix instead of the GEMM")
     args = ap.parse_args()
 
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.op != "gemm":
+        byte_kernel_arm(args)
         return
     if args.gpus > 1 and "RANK" not in os.environ:
         # started by hand without a launcher: re-enter under torch.distributed.run
