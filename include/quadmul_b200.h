@@ -51,7 +51,9 @@ typedef struct qm_gemm_opts {
     int cta_pair;   /* 0 = table, 1 = single-CTA MMA, 2 = two-CTA (cta_group::2) MMA            */
     int a_tmem;     /* 0 = table, 1 = operand A from shared memory, 2 = operand A from TMEM
                        (only with tile_n 256, cta_pair 2, no swap, no split)                    */
-    int reserved[2];
+    int plain_stores; /* 1 = write C with ordinary vector stores only (no TMA store); for a C that lives in
+                         another GPU's memory (peer mapping), as the fused gather of the sharded driver uses */
+    int reserved[1];
 } qm_gemm_opts_t;
 
 const char *qm_status_string(int status);
@@ -86,6 +88,10 @@ int qm_gemm_s4_ex(const void *A, const void *B, void *C, int m, int n, int k, vo
  */
 int qm_gemm_s4_ldc(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc,
                    void *stream);
+
+/* qm_gemm_s4_ldc with options (see qm_gemm_opts_t). */
+int qm_gemm_s4_ldc_ex(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc,
+                      void *stream, const qm_gemm_opts_t *opts);
 
 /*
  * HOST-buffer form for FFI callers that hold plain memory: copies A and B to the device, runs

@@ -26,7 +26,8 @@ class GemmOpts(ctypes.Structure):
         ("split_k", _i),
         ("cta_pair", _i),
         ("a_tmem", _i),
-        ("reserved", _i * 2),
+        ("plain_stores", _i),
+        ("reserved", _i * 1),
     ]
 
 
@@ -39,6 +40,7 @@ SIGNATURES = {
     "qm_gemm_s4": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "qm_gemm_s4_ex": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, ctypes.POINTER(GemmOpts)]),
     "qm_gemm_s4_ldc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i64, _vp]),
+    "qm_gemm_s4_ldc_ex": (_i, [_vp, _vp, _vp, _i, _i, _i, _i64, _vp, ctypes.POINTER(GemmOpts)]),
     "qm_gemm_s4_host": (_i, [_vp, _vp, _vp, _i, _i, _i]),
     "qm_pack_s4": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "qm_unpack_s4": (_i, [_vp, _vp, _i64, _i64, _vp]),

@@ -94,6 +94,7 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
     if (st != QM_OK) return st;
     GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), static_cast<int32_t *>(C), m, n, k, ldc,
                static_cast<cudaStream_t>(stream)};
+    g.plain_stores = opts && opts->plain_stores != 0;
     if (k == 0) {  // empty sum: C = 0
         cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)n * 4, (size_t)m, g.stream);
         return e == cudaSuccess ? QM_OK : record_cuda_error(e, "cudaMemset2DAsync");
@@ -200,6 +201,12 @@ int qm_gemm_s4_ex(const void *A, const void *B, void *C, int m, int n, int k, vo
 int qm_gemm_s4_ldc(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc, void *stream)
 {
     return gemm_dispatch(A, B, C, m, n, k, ldc, stream, nullptr);
+}
+
+int qm_gemm_s4_ldc_ex(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc, void *stream,
+                      const qm_gemm_opts_t *opts)
+{
+    return gemm_dispatch(A, B, C, m, n, k, ldc, stream, opts);
 }
 
 int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int k)

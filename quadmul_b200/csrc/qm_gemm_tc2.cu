@@ -591,7 +591,7 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
     // TMA store of C needs a 16-byte-aligned base and row pitch; otherwise the kernel stores with plain vectors
     static const bool allow_tma_store = !std::getenv("QM_NO_TMA_STORE");
     const int use_tma_store =
-        (allow_tma_store && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && g.ldc < (1ll << 36)) ? 1 : 0;
+        (allow_tma_store && !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && g.ldc < (1ll << 36)) ? 1 : 0;
     CUtensorMap tmC = tmA;  // placeholder when unused
     if (use_tma_store) {
         st = make_tmap_c(&tmC, g.C, g.m, g.n, g.ldc);

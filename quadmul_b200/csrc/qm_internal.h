@@ -41,6 +41,7 @@ struct GemmArgs {
     int m, n, k;
     int64_t ldc;
     cudaStream_t stream;
+    bool plain_stores = false;  // write C with ordinary vector stores only (destination in another GPU's memory)
 };
 
 // Resolved tensor-path plan (see qm_tile_table.h for how it is chosen).

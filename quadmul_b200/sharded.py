@@ -46,9 +46,10 @@ class NShardedGemm:
         return b_full[self.begin : self.begin + self.count]
 
     # -- local product -----------------------------------------------------------------
-    def local(self, a, b_shard, m: int, k: int, out=None):
+    def local(self, a, b_shard, m: int, k: int, out=None, plain_stores: bool = False):
         """C[:, begin:begin+count] = A @ b_shard^T on this rank's device. `out` may be a padded
-        [m, slab_stride] buffer; the slab is written into its first `count` columns."""
+        [m, slab_stride] buffer; the slab is written into its first `count` columns.  `plain_stores`
+        is for an `out` that is a view of ANOTHER GPU's memory (see SymmetricC)."""
         import torch
 
         if b_shard.shape[0] != self.count:
@@ -62,22 +63,36 @@ class NShardedGemm:
         if self._gemm_fn is not None:
             self._gemm_fn(a, b_shard, out, m, self.count, k)
         else:
-            self._gemm_ldc(a, b_shard, out, m, k)
+            self._gemm_ldc(a, b_shard, out, m, k, plain_stores)
         return out
 
-    def _gemm_ldc(self, a, b_shard, out, m, k):
+    def _gemm_ldc(self, a, b_shard, out, m, k, plain_stores=False):
+        import ctypes
+
         import quadmul_b200 as qm
-        from ._lib import LIB, check
+        from ._lib import LIB, GemmOpts, check
 
         if not (a.is_cuda and b_shard.is_cuda and out.is_cuda):
             raise ValueError("NShardedGemm.local: CUDA tensors required (there is no CPU path)")
         if out.stride(1) != 1 or not a.is_contiguous() or not b_shard.is_contiguous():
             raise ValueError("NShardedGemm.local: operands must be contiguous, out row-major")
+        opts = GemmOpts(plain_stores=1 if plain_stores else 0)
         with qm._on_device(a):
-            st = LIB.qm_gemm_s4_ldc(a.data_ptr(), b_shard.data_ptr(), out.data_ptr(), m, self.count, k, out.stride(0),
-                                    qm._stream_of(a))
+            st = LIB.qm_gemm_s4_ldc_ex(a.data_ptr(), b_shard.data_ptr(), out.data_ptr(), m, self.count, k, out.stride(0),
+                                       qm._stream_of(a), ctypes.byref(opts))
         check(st, f"sharded gemm rank {self.rank}")
         qm._launches += 1
+
+    # -- fused gather: the GEMM epilogue writes straight into the destination rank's C ------------
+    def local_into(self, a, b_shard, m: int, k: int, c_sym: "SymmetricC", dst: int = 0):
+        """Compute this rank's column slab and store it, from inside the GEMM kernel, into rank `dst`'s
+        full-width C (peer-mapped memory, ordinary stores over NVLink; no staging, no NCCL).  Call
+        `c_sym.barrier()` afterwards: it returns once every rank's kernel has finished writing."""
+        target = c_sym.on_rank(dst)
+        if tuple(target.shape) != (m, self.n):
+            raise ValueError("SymmetricC shape does not match (m, n)")
+        return self.local(a, b_shard, m, k, out=target[:, self.begin : self.begin + self.count],
+                          plain_stores=(dst != self.rank))
 
     # -- optional collective -------------------------------------------------------------
     def gather(self, slab, m: int, out=None):
@@ -108,3 +123,31 @@ class NShardedGemm:
 
             unshard_c(slabs, out, m, self.n, self.world, self.slab_stride)
         return out
+
+
+class SymmetricC:
+    """A full-width C [m, n] (int32) allocated collectively so that every rank can address every rank's copy.
+
+    Uses torch's symmetric memory (CUDA virtual-memory handles exchanged inside one node).  `local` is this
+    rank's copy, `on_rank(r)` a tensor view of rank r's copy mapped into this process."""
+
+    def __init__(self, m: int, n: int, group=None, device=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.m, self.n = int(m), int(n)
+        self.group = group if group is not None else dist.group.WORLD
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm.empty((self.m, self.n), dtype=torch.int32, device=device)
+        self.handle = symm.rendezvous(self.local, self.group)
+
+    def on_rank(self, r: int):
+        import torch
+
+        return self.handle.get_buffer(int(r), (self.m, self.n), torch.int32)
+
+    def barrier(self):
+        """All ranks' earlier work on the current streams is complete when this returns on the stream."""
+        self.handle.barrier()

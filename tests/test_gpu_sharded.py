@@ -72,6 +72,20 @@ def _nccl_worker(rank, world, port, m, n, k, q):
         torch.cuda.synchronize()
         want = o.gemm(ap, bp)
         ok = bool(np.array_equal(full.cpu().numpy(), want))
+        # fused gather: every rank's GEMM epilogue stores its slab into rank 0's C over NVLink
+        from quadmul_b200.sharded import SymmetricC
+
+        csym = SymmetricC(m, n)
+        csym.local.fill_(-3)
+        csym.barrier()
+        sh.local_into(a, b, m, k, csym, dst=0)
+        csym.barrier()
+        torch.cuda.synchronize()
+        if rank == 0:
+            ok = ok and bool(np.array_equal(csym.local.cpu().numpy(), want))
+        else:
+            ok = ok and bool((csym.local == -3).all())  # nobody wrote into the other ranks' copies
+        dist.barrier()
         code, _ = qm.device_status()
         q.put((rank, ok and code == 0))
     finally:
