@@ -263,10 +263,13 @@ def native_arm(args) -> None:
     qm.init()
 
     custom = args.shape is not None
+    large = args.workload == "large"
     if custom:
         if world != 1:
             raise SystemExit("bench.py: --shape is a single-GPU option")
         m, n_total, k = (int(x) for x in args.shape.split(","))
+    elif large:
+        m = n_total = k = 32768
     else:
         m, n_total, k = M, N_PER_GPU * world, K
     forced = dict(tile_n=args.tile_n, swap_ab=args.swap_ab, cta_pair=args.cta_pair, split_k=args.split_k, a_tmem=args.a_tmem)
@@ -289,12 +292,25 @@ def native_arm(args) -> None:
         torch.cuda.synchronize()
 
     counter = [0]
+    csym = full_c = None
+    if large and args.gather == "fused" and world > 1:
+        from quadmul_b200.sharded import SymmetricC
+
+        csym = SymmetricC(m, n_total)
+    if large and args.gather == "nccl" and world > 1:
+        full_c = torch.empty((m, n_total), dtype=torch.int32, device="cuda")
 
     def launch():
         i = counter[0] % rotate
         counter[0] += 1
         if forced:
             qm.gemm_ex(a, bs[i], cs[i], m, n_local, k, kernel=1, **forced)
+        elif csym is not None:
+            sh.local_into(a, bs[i], m, k, csym, dst=0)  # epilogue stores go to rank 0's C over NVLink
+            csym.barrier()
+        elif full_c is not None:
+            sh.local(a, bs[i], m, k, out=cs[i])
+            sh.gather(cs[i], m, out=full_c)
         else:
             sh.local(a, bs[i], m, k, out=cs[i])
 
@@ -369,6 +385,10 @@ def native_arm(args) -> None:
             "algorithmic_bytes_per_launch": per_launch_bytes,
         })
         cfg = config(world)
+        if large:
+            cfg.update({"workload": f"int4 GEMM M=N=K=32768, B column-sharded over {world} GPU(s), A replicated; gather: {args.gather}",
+                        "m": m, "n_total": n_total, "k": k, "parallelism": f"n-shard x{world}, gather={args.gather}",
+                        "l2": "working set exceeds the 126 MB L2 many times over"})
         if custom:
             cfg.update({"workload": f"int4 GEMM M={m} N={n_total} K={k} (single GPU, not the headline case)", "m": m,
                         "n_total": n_total, "k": k})
@@ -377,7 +397,7 @@ def native_arm(args) -> None:
         if args.graph:
             cfg["cuda_graph_launches_per_step"] = launches_per_step
         line = {
-            "metric": METRIC if not custom else f"int4 GEMM TOPS at M={m} N={n_total} K={k}",
+            "metric": METRIC if not (custom or large) else f"int4 GEMM TOPS at M={m} N={n_total} K={k}",
             "value": value,
             "unit": UNIT,
             "n_gpus": world,
@@ -385,7 +405,7 @@ def native_arm(args) -> None:
             "warmup": warmup,
             "ms_per_step": ms_per_step,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong" if large else "weak",
             "vs_baseline": None,
             "dtype": "s4 x s4 -> s32 (tcgen05 kind::i8, exact)",
             "data": "synthetic",
@@ -397,7 +417,7 @@ def native_arm(args) -> None:
         }
 
     # ---- end to end through the host-buffer C-ABI call, copies inside the timed region ----
-    if not args.no_e2e:
+    if not args.no_e2e and not large:
         ha = a.cpu().pin_memory()
         hb = bs[0].cpu().pin_memory()
         hc = torch.empty((m, n_local), dtype=torch.int32).pin_memory()
@@ -424,7 +444,7 @@ def native_arm(args) -> None:
             }
             line["gpu_launches"] += e2e_steps + 1
 
-    if rank == 0 and world == 1 and not custom and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not custom and not large and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_port()
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -495,6 +515,10 @@ def main() -> None:
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--a-tmem", type=int, default=0)
     ap.add_argument("--graph", type=int, default=0, help="capture this many launches per step in one CUDA graph")
+    ap.add_argument("--workload", choices=["headline", "large"], default="headline",
+                    help="large: M=N=K=32768 with B column-sharded over the GPUs (strong scaling)")
+    ap.add_argument("--gather", choices=["none", "nccl", "fused"], default="none",
+                    help="with --workload large: also bring the full C to every rank (nccl) or to rank 0 (fused) inside each step")
     ap.add_argument("--op", choices=["gemm", "pack", "unpack"], default="gemm",
                     help="pack / unpack: time the HBM-bound byte kernels on a --shape ROWS,K matrix instead of the GEMM")
     args = ap.parse_args()
