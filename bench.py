@@ -146,7 +146,7 @@ def physical_gpu_index(local_index: int) -> int:
 # ------------------------------------------------------------------------------------------
 # CPU legs (the only places that touch oracle/)
 # ------------------------------------------------------------------------------------------
-def cpu_baseline_port(rows: int = 4096) -> dict:
+def cpu_baseline_port(rows: int = 8192) -> dict:
     """The oracle (CPU restatement, OpenMP) on rows [0, rows) of the 8192^3 product."""
     from oracle import oracle as o
 
