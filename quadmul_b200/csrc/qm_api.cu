@@ -20,9 +20,13 @@ DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mutex;
 thread_local std::string t_last_error;
 
-struct HostStage {  // grow-only device buffers of qm_gemm_s4_host
+constexpr int kHostSlabs = 8;  // row slabs whose result copy overlaps the next slab's upload and GEMM
+struct HostStage {             // grow-only device buffers, copy stream and events of qm_gemm_s4_host
     void *a = nullptr, *b = nullptr, *c = nullptr;
     size_t a_bytes = 0, b_bytes = 0, c_bytes = 0;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t slab_done[kHostSlabs] = {};
+    bool streams_ready = false;
 };
 HostStage g_stage[kMaxDevices];
 
@@ -234,15 +238,44 @@ int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int 
     if ((e = grow(s.b, s.b_bytes, b_bytes ? b_bytes : 16)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(B)");
     if ((e = grow(s.c, s.c_bytes, c_bytes)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(C)");
     cudaStream_t stream = cudaStreamPerThread;
-    if (a_bytes && (e = cudaMemcpyAsync(s.a, hA, a_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
-        return record_cuda_error(e, "cudaMemcpyAsync(A)");
     if (b_bytes && (e = cudaMemcpyAsync(s.b, hB, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
         return record_cuda_error(e, "cudaMemcpyAsync(B)");
-    st = gemm_dispatch(s.a, s.b, s.c, m, n, k, n, stream, nullptr);
-    if (st != QM_OK) return st;
-    if ((e = cudaMemcpyAsync(hC, s.c, c_bytes, cudaMemcpyDeviceToHost, stream)) != cudaSuccess)
-        return record_cuda_error(e, "cudaMemcpyAsync(C)");
+    // Large results: cut C into row slabs and copy slab i back on a second stream while slab i+1 is uploaded and
+    // computed, so the two PCIe directions and the GEMM overlap.  Small ones: one upload, one GEMM, one download.
+    const int slabs = (c_bytes >= (32u << 20) && m >= 256 * kHostSlabs) ? kHostSlabs : 1;
+    if (slabs > 1 && !s.streams_ready) {
+        if ((e = cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking)) != cudaSuccess)
+            return record_cuda_error(e, "cudaStreamCreate");
+        for (int i = 0; i < kHostSlabs; ++i)
+            if ((e = cudaEventCreateWithFlags(&s.slab_done[i], cudaEventDisableTiming)) != cudaSuccess)
+                return record_cuda_error(e, "cudaEventCreate");
+        s.streams_ready = true;
+    }
+    const int rows_per_slab = slabs > 1 ? ((m / slabs + 255) / 256) * 256 : m;
+    const size_t row_a = (size_t)(k / 2), row_c = (size_t)n * 4;
+    for (int i = 0, r0 = 0; r0 < m; ++i, r0 += rows_per_slab) {
+        const int rows = (m - r0 < rows_per_slab) ? m - r0 : rows_per_slab;
+        char *dA = static_cast<char *>(s.a) + (size_t)r0 * row_a;
+        char *dC = static_cast<char *>(s.c) + (size_t)r0 * row_c;
+        if (row_a && (e = cudaMemcpyAsync(dA, static_cast<const char *>(hA) + (size_t)r0 * row_a, (size_t)rows * row_a,
+                                          cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+            return record_cuda_error(e, "cudaMemcpyAsync(A)");
+        st = gemm_dispatch(dA, s.b, dC, rows, n, k, n, stream, nullptr);
+        if (st != QM_OK) return st;
+        cudaStream_t out_stream = stream;
+        if (slabs > 1) {
+            if ((e = cudaEventRecord(s.slab_done[i % kHostSlabs], stream)) != cudaSuccess) return record_cuda_error(e, "cudaEventRecord");
+            if ((e = cudaStreamWaitEvent(s.copy_stream, s.slab_done[i % kHostSlabs], 0)) != cudaSuccess)
+                return record_cuda_error(e, "cudaStreamWaitEvent");
+            out_stream = s.copy_stream;
+        }
+        if ((e = cudaMemcpyAsync(static_cast<char *>(hC) + (size_t)r0 * row_c, dC, (size_t)rows * row_c, cudaMemcpyDeviceToHost,
+                                 out_stream)) != cudaSuccess)
+            return record_cuda_error(e, "cudaMemcpyAsync(C)");
+    }
     if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return record_cuda_error(e, "cudaStreamSynchronize");
+    if (slabs > 1 && (e = cudaStreamSynchronize(s.copy_stream)) != cudaSuccess)
+        return record_cuda_error(e, "cudaStreamSynchronize(copy)");
     int code = 0;
     if ((e = cudaMemcpy(&code, ctx->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
         return record_cuda_error(e, "cudaMemcpy(status)");

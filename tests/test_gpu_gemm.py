@@ -200,6 +200,37 @@ def test_host_buffer_entry_point(qm, cuda_clean, oracle):
     assert np.array_equal(c, oracle.gemm(ap, bp))
 
 
+def test_host_buffer_entry_point_large_is_pipelined_in_row_slabs(qm, cuda_clean, oracle):
+    """Above 32 MiB of C the host entry point uploads, multiplies and downloads in 8 row slabs on two streams."""
+    torch = cuda_clean
+    m, n, k = 2304, 4096, 512  # 36 MiB of C, slabs of 512 rows with a shorter last one
+    a = qm.fill_packed(m, k, 17); b = qm.fill_packed(n, k, 18)
+    want = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    qm.gemm(a, b, want, m, n, k)
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    hc = torch.zeros((m, n), dtype=torch.int32).pin_memory()
+    for _ in range(2):
+        hc.zero_()
+        qm.gemm_host(ha, hb, hc, m, n, k)
+        assert torch.equal(hc, want.cpu())
+    ap = ha.numpy().view(np.uint8); bp = hb.numpy().view(np.uint8)
+    assert np.array_equal(hc[2200:2304].numpy(), oracle.gemm(ap, bp, rows=(2200, 2304)))
+
+
+def test_fuzz_small_shapes_every_path(qm, cuda_clean, oracle):
+    """Seeded random shapes through the table's choice and through explicit tiles; all bit-exact."""
+    rng = np.random.default_rng(2024)
+    for trial in range(40):
+        m = int(rng.integers(1, 400)); n = int(rng.integers(1, 600)); k = int(rng.integers(1, 40)) * 32
+        ap = oracle.fill_packed(m, k, 100 + trial); bp = oracle.fill_packed(n, k, 200 + trial)
+        want = oracle.gemm(ap, bp)
+        variants = [{}, tc(int(rng.choice([16, 32, 64, 128, 256])), 1, 1), tc(int(rng.choice([16, 32, 64, 128])), 2, 1),
+                    tc(int(rng.choice([128, 256])), 1, 2), dict(kernel=1, tile_n=256, swap_ab=1, cta_pair=2, a_tmem=2), SIMT]
+        for opts in variants:
+            got = run_gemm(qm, cuda_clean, ap, bp, **opts)
+            assert np.array_equal(got, want), f"{m}x{n}x{k} {opts}: " + mismatch_report(got, want)
+
+
 def test_wrapper_symbol_and_current_stream(qm, cuda_clean, oracle):
     torch = cuda_clean
     from quadmul_b200 import _lib
