@@ -116,18 +116,22 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
             opts->tile_n < 0)
             return QM_ERR_ARG;
         // the table's K split belongs to the table's tile form: an explicit form starts unsplit
-        if (opts->swap_ab || opts->tile_n || opts->cta_pair) p.split_k = 1;
+        if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem) p.split_k = 1;
         if (opts->swap_ab) p.swap_ab = opts->swap_ab - 1;
         if (opts->tile_n) p.tile_n = opts->tile_n;
         if (opts->split_k) p.split_k = opts->split_k;
         if (opts->cta_pair) p.cta_pair = opts->cta_pair;
         if (opts->a_tmem < 0 || opts->a_tmem > 2) return QM_ERR_ARG;
         if (opts->a_tmem) p.a_tmem = opts->a_tmem - 1;
-        else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->split_k) p.a_tmem = 0;
+        else if (opts->swap_ab || opts->tile_n || opts->cta_pair) p.a_tmem = 0;
     }
     if (p.a_tmem) {
-        if (p.swap_ab || p.tile_n != 256 || p.cta_pair != 2 || p.split_k != 1) return QM_ERR_ARG;
-        return tc2_launch(g, *ctx);
+        if (p.swap_ab || p.tile_n != 256 || p.cta_pair != 2) return QM_ERR_ARG;
+        if (p.split_k > 1 && !tc2_can_split(g)) {
+            if (opts && opts->split_k) return QM_ERR_ALIGN;
+            p.split_k = 1;
+        }
+        return tc2_launch(g, *ctx, p.split_k);
     }
     if (p.split_k > 1 && !(opts && opts->split_k) &&
         (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))

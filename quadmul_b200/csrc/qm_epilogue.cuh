@@ -72,6 +72,16 @@ __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t smem_src
                  : "memory");
 }
 
+// Same transfer, but the 32-bit integers are ADDED to what global memory holds (exact and order-independent for
+// int32, so K partitions of a tile can accumulate into one C that starts at zero).
+__device__ __forceinline__ void tma_reduce_add_2d(const void *tmap, uint32_t smem_src, int32_t x, int32_t y)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(smem_src)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int kPending>
@@ -85,7 +95,7 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // v[j] = 256 * block[lane][j]; `buf` is this warp's buffer for this block (1024-byte aligned);
 // `first_use` is false once the buffer has been handed to the TMA engine before.
 __device__ __forceinline__ void store_block_tma(const uint32_t (&v)[32], uint32_t buf, int lane, const void *tmapC, int col0,
-                                                int row0, bool reuse)
+                                                int row0, bool reuse, bool accumulate = false)
 {
     if (reuse) {
         if (lane == 0) tma_store_wait_read<1>();  // at most the other buffer's store may still be reading
@@ -104,7 +114,8 @@ __device__ __forceinline__ void store_block_tma(const uint32_t (&v)[32], uint32_
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_2d(tmapC, buf, col0, row0);
+        if (accumulate) tma_reduce_add_2d(tmapC, buf, col0, row0);
+        else tma_store_2d(tmapC, buf, col0, row0);
         tma_store_commit();
     }
 }

@@ -167,7 +167,7 @@ template <int H, bool MC>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                 const __grid_constant__ CUtensorMap tmapC, int use_tma_store, int32_t *__restrict__ C, int64_t ldc, int M,
-                int N, int K, int *status)
+                int N, int K, int *status, int split_k)
 {
     using Cfg = Tc2Cfg<H>;
     constexpr int S = Cfg::S, SP = Cfg::SP;
@@ -191,8 +191,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     const uint32_t cta_rank = cluster_ctarank();
     const int unit = (int)(blockIdx.x >> 1), num_units = (int)(gridDim.x >> 1);
     const int tilesP = (M + 255) / 256, tilesQ = (N + kBN - 1) / kBN;
-    const int num_tiles = tilesP * tilesQ;
-    const int num_kb = (K + H * kSubK - 1) / (H * kSubK);  // stages per tile; TMA zero-fills beyond K
+    // A work item is one K partition of one tile; with split_k > 1 the partitions add into a C the host zeroed.
+    const int num_tiles = tilesP * tilesQ * split_k;
+    const int num_kb_total = (K + H * kSubK - 1) / (H * kSubK);  // stages per tile; TMA zero-fills beyond K
+    auto kb_begin = [&](int item) { return (int)(((long long)(item % split_k) * num_kb_total) / split_k); };
+    auto kb_end = [&](int item) { return (int)(((long long)(item % split_k + 1) * num_kb_total) / split_k); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SP; ++s) {
@@ -234,10 +237,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
-                tile_coords2(t, tilesP, tilesQ, tp, tq);
+                tile_coords2(t / split_k, tilesP, tilesQ, tp, tq);
                 const int yA = tp * 256 + (int)cta_rank * kRowsA;
                 const int yB = tq * kBN + (int)cta_rank * kRowsB;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                     const int s = it % SP;
                     const uint32_t ph = (it / SP) & 1u;
                     if (!mbar_wait(pk_empty(s), ph ^ 1u, abort_flag)) {
@@ -276,7 +279,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 }
                 PROF(0)
                 tc_fence_after_sync();
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb0 = kb_begin(t);
+                for (int kb = kb0, kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
                     if (!mbar_wait(cv_full(s), ph, abort_flag)) {
@@ -293,7 +297,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         const uint32_t ta = tmem_a0 + (uint32_t)(s * Cfg::kAStageCols + h * kASubCols);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)
-                            umma_i8_ta(tmem_base, ta + 8u * k4, dB + 2u * k4, kIdesc, (kb | h | k4) != 0 ? 1u : 0u);
+                            umma_i8_ta(tmem_base, ta + 8u * k4, dB + 2u * k4, kIdesc, (kb != kb0 || (h | k4) != 0) ? 1u : 0u);
                     }
                     if constexpr (MC) {
                         umma_commit_pair(cv_empty(s));
@@ -329,7 +333,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         PROF_DECL
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
-            tile_coords2(t, tilesP, tilesQ, tp, tq);
+            tile_coords2(t / split_k, tilesP, tilesQ, tp, tq);
             PROF(2)
             const bool ok = warp_wait<false>(acc_full, lt & 1u, abort_flag, lane);
             PROF(0)
@@ -350,7 +354,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the buffer
                         __syncwarp();
                     }
-                    store_block_tma(v, buf, lane, &tmapC, col, row0, false);
+                    store_block_tma(v, buf, lane, &tmapC, col, row0, false, split_k > 1);
                     buf_used = true;
                 } else {
                     uint32_t h0[16], h1[16];
@@ -392,7 +396,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         bool ok = true;
         PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                 const int ps = it % SP, cs = it % S;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
                 PROF(4)
@@ -456,7 +460,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         bool ok = true;
         PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                 const int ps = it % SP, cs = it % S;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
                 PROF(4)
@@ -577,7 +581,7 @@ int make_tmap_c(CUtensorMap *map, const int32_t *C, int m, int n, int64_t ldc)
 }
 
 template <int H, bool MC>
-int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
+int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
     auto kernel = gemm_tc2_kernel<H, MC>;
     const int64_t kbytes = g.k / 2;
@@ -586,7 +590,9 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
     if (st != QM_OK) return st;
     st = make_tmap2(&tmB, g.B, g.n, kbytes, kRowsB, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (st != QM_OK) return st;
-    const int64_t tiles = (int64_t)((g.m + 255) / 256) * ((g.n + kBN - 1) / kBN);
+    const int num_kb = (g.k + H * kSubK - 1) / (H * kSubK);
+    if (split_k < 1 || split_k > num_kb) return QM_ERR_ARG;
+    const int64_t tiles = (int64_t)((g.m + 255) / 256) * ((g.n + kBN - 1) / kBN) * split_k;
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
     // TMA store of C needs a 16-byte-aligned base and row pitch; otherwise the kernel stores with plain vectors
     static const bool allow_tma_store = !std::getenv("QM_NO_TMA_STORE");
@@ -596,6 +602,12 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
     if (use_tma_store) {
         st = make_tmap_c(&tmC, g.C, g.m, g.n, g.ldc);
         if (st != QM_OK) return st;
+    }
+    if (split_k > 1) {
+        // the K partitions accumulate with TMA reduce-add: needs the TMA path and a C that starts at zero
+        if (!use_tma_store) return QM_ERR_ALIGN;
+        cudaError_t me = cudaMemset2DAsync(g.C, (size_t)g.ldc * 4, 0, (size_t)g.n * 4, (size_t)g.m, g.stream);
+        if (me != cudaSuccess) return record_cuda_error(me, "cudaMemset2DAsync(C)");
     }
 
     cudaLaunchConfig_t cfg = {};
@@ -624,7 +636,7 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx)
     if (units < 1) units = 1;
     if (tiles < units) units = (int)tiles;
     cfg.gridDim = dim3((unsigned)(units * 2), 1, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc2_kernel launch");
     return QM_OK;
 }
@@ -647,14 +659,19 @@ int tc2_prepare_device()
 // Variant: sub-blocks per stage (1 or 2) and one pair-wide commit (1) or two single commits (0).
 // Measured at 8192^3 on B200: "10" 442 us, "11" 418 us, "20" 337 us, "21" 328 us (before the TMA-store
 // epilogue; 303 us with it), so "21" is the default.  The environment variable QM_TC2_VARIANT overrides it.
-int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx)
+bool tc2_can_split(const GemmArgs &g)
+{
+    return !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && !std::getenv("QM_NO_TMA_STORE");
+}
+
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
     static const int variant = []() {
         const char *e = std::getenv("QM_TC2_VARIANT");
         return (e && (e[0] == '1' || e[0] == '2') && (e[1] == '0' || e[1] == '1')) ? (e[0] - '0') * 10 + (e[1] - '0') : 21;
     }();
 #define X(H, MC) \
-    if (variant == H * 10 + (MC ? 1 : 0)) return tc2_launch_variant<H, MC>(g, ctx);
+    if (variant == H * 10 + (MC ? 1 : 0)) return tc2_launch_variant<H, MC>(g, ctx, split_k);
     QM_TC2_FOR_EACH(X)
 #undef X
     return QM_ERR_ARG;

@@ -63,7 +63,8 @@ int tc_counters_needed(int m, int n, const TcPlan &p);
 
 // qm_gemm_tc2.cu: 256 x 256 pair tile, A through TMEM
 int tc2_prepare_device();
-int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx);
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k);
+bool tc2_can_split(const GemmArgs &g);  // K partitions accumulate through TMA reduce-add: needs an aligned local C
 
 // qm_gemm_simt.cu
 int simt_launch(const GemmArgs &g);

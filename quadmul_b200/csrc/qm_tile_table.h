@@ -14,7 +14,7 @@ struct PlanRule {
     int cta_pair; // 1 or 2
 };
 
-// Ordered by m_max.  Decode-sized m puts the weights on the M axis so that a 128-row MMA is fully
+// Ordered by m_max.  Decode-sized m (<= 64) puts the weights on the M axis so that a 128-row MMA is fully
 // used by weight rows and only `tile_n` (>= m) columns are spent on tokens.  Everything larger runs
 // the 256 x 256 CTA-pair tile: measured on B200 it beats the single-CTA 128 x 256 and both 128-wide
 // forms at 8192^3 and at all four M = 2048 prefill shapes (python -m quadmul_b200.tune), because
@@ -23,7 +23,6 @@ static const PlanRule kPlanRules[] = {
     {16, 1, 16, 1},
     {32, 1, 32, 1},
     {64, 1, 64, 1},
-    {128, 1, 128, 1},
     {0x7FFFFFFF, 0, 256, 2},
 };
 
@@ -63,7 +62,20 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
         if (p.cta_pair == 2 && p.tile_n < 128) p.cta_pair = 1;
         // the 256 x 256 pair tile takes operand A through TMEM (gemm_tc2_kernel): 3.5 POPS against 2.3 POPS
         // for the all-shared-memory pair tile at 8192^3
-        if (p.cta_pair == 2 && p.tile_n == 256) p.a_tmem = 1;
+        if (p.cta_pair == 2 && p.tile_n == 256) {
+            p.a_tmem = 1;
+            // Few tiles (short M and N): cut K so that more CTA pairs work; the partitions add into a zeroed C with
+            // TMA reduce-add.  Measured: 128..256 x 4096 x 4096 (16 tiles) 17.1 -> 14.2 us with 4 partitions,
+            // x 8192 x 8192 (32 tiles) 26.1 -> 21.2 us with 2; no gain once the tiles fill half of the pairs.
+            const int tiles = ((m + 255) / 256) * ((n + 255) / 256);
+            const int pairs = num_sms / 2, stages = (k + 255) / 256;
+            if (tiles * 2 <= pairs) {
+                int sk = pairs / tiles;
+                if (sk > 4) sk = 4;
+                if (sk > stages / 2) sk = stages / 2;
+                p.split_k = sk < 1 ? 1 : sk;
+            }
+        }
     }
     return p;
 }

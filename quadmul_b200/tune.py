@@ -24,12 +24,14 @@ def variants(m: int, n: int):
     if m <= 256:
         for tn in (16, 32, 64, 128):
             if tn >= min(m, 128) or tn == 128:
-                for sk in (1, 2, 3, 4, 6, 8, 16):
+                for sk in ((1, 2, 3, 4, 6, 8, 16) if m <= 64 else (1, 2, 4)):
                     out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk))
     if m > 64:
         for tn in (128, 256):
             out.append(dict(tile_n=tn, swap_ab=1, cta_pair=1, split_k=1))
             out.append(dict(tile_n=tn, swap_ab=1, cta_pair=2, split_k=1))
+        for sk in (1, 2, 3, 4, 6, 8):  # pair tile with A through TMEM; K partitions add into C with TMA reduce
+            out.append(dict(tile_n=256, swap_ab=1, cta_pair=2, split_k=sk, a_tmem=2))
     return out
 
 

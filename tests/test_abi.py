@@ -77,6 +77,7 @@ def test_plan(qm):
 
     p = qm.plan(8192, 8192, 8192)
     assert p["kernel"] == _lib.QM_KERNEL_TC and p["tile_n"] == 256 and p["swap_ab"] == 1 and p["cta_pair"] == 2 and p["a_tmem"] == 2
+    assert qm.plan(128, 4096, 4096)["a_tmem"] == 2 and qm.plan(128, 4096, 4096)["split_k"] == 4
     d = qm.plan(16, 4096, 4096)
     assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0

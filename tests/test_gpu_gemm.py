@@ -68,6 +68,17 @@ def test_pair_tile_with_a_in_tmem(qm, cuda_clean, oracle, golden):
         _check(qm, cuda_clean, oracle, ap, bp, **opts)
 
 
+@pytest.mark.parametrize("split_k", [2, 3, 4])
+def test_pair_tile_split_k_with_tma_reduce(qm, cuda_clean, oracle, split_k):
+    """gemm_tc2_kernel with K partitions: every partition adds its partial tile into a zeroed C (TMA reduce-add)."""
+    opts = dict(kernel=1, tile_n=256, swap_ab=1, cta_pair=2, a_tmem=2, split_k=split_k)
+    for m, n, k in [(128, 1024, 4096), (300, 520, 1056), (512, 4096, 2048), (257, 8, 1024)]:
+        ap = oracle.fill_packed(m, k, 71); bp = oracle.fill_packed(n, k, 72)
+        want = oracle.gemm(ap, bp)
+        for _ in range(2):
+            _check(qm, cuda_clean, oracle, ap, bp, want=want, **opts)
+
+
 @pytest.mark.parametrize("split_k", [2, 3, 4, 8])
 def test_split_k_through_scratch(qm, cuda_clean, oracle, golden, split_k):
     """K partitions of a tile write partial tiles to scratch; the last one to arrive sums them.
