@@ -33,12 +33,14 @@
 #include "qm_epilogue.cuh"
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
+#include "qm_tc_common.cuh"
 
 namespace qm {
 
 namespace {
 
 using namespace ptx;
+using namespace tc;
 
 constexpr int kNumConvWarps = 8;
 constexpr int kFirstEpiWarp = 2;
@@ -50,7 +52,6 @@ constexpr int kKBlock = 128;            // K elements per stage
 constexpr int kPkRowBytes = kKBlock / 2;  // 64
 constexpr int kCvRowBytes = kKBlock;      // 128
 constexpr int kStageBudget = 200 * 1024;
-constexpr int kRasterGroup = 8;
 
 constexpr int next_pow2(int x)
 {
@@ -86,31 +87,6 @@ struct TcCfg {
     static_assert(kSmemBytes <= 232448, "shared memory");
     static_assert(kPkStage % 1024 == 0 && kCvStage % 1024 == 0, "stage alignment");
 };
-
-// Static tile order: groups of kRasterGroup P-tiles, P fastest inside a group, so the tiles in
-// flight at one time share operand rows in L2.
-__device__ __forceinline__ void tile_coords(int t, int tilesP, int tilesQ, int &tp, int &tq)
-{
-    const int per_group = kRasterGroup * tilesQ;
-    const int g = t / per_group, rem = t - g * per_group;
-    const int p0 = g * kRasterGroup;
-    const int gsz = min(kRasterGroup, tilesP - p0);
-    tq = rem / gsz;
-    tp = p0 + (rem - tq * gsz);
-}
-
-__device__ __forceinline__ void report_timeout(int *status, int site)
-{
-    if (atomicCAS(status, 0, (int)QM_ERR_TIMEOUT) == 0) status[1] = site | ((int)blockIdx.x << 8);
-}
-
-// K-major, 128-byte rows, 8-row groups 1024 bytes apart, SWIZZLE_128B, descriptor version 1.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
-{
-    const uint32_t lo = ((addr & 0x3FFFFu) >> 4) | (1u << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
-}
 
 template <int BN, bool SWAP, int G>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -408,19 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                 for (int j = 0; j < Cfg::kItemIters; ++j) {
                     const int i = j * kConvThreads + ctid;
                     if (Cfg::kItems % kConvThreads == 0 || i < Cfg::kItems) {
-                        const int r = i >> 2, c = i & 3;
-                        const uint32_t d = dst + r * kCvRowBytes + (((2 * c) ^ (r & 7)) << 4);
-                        uint4 lo, hi;
-                        lo.x = (w[j].x << 4) & 0xF0F0F0F0u;
-                        lo.y = (w[j].y << 4) & 0xF0F0F0F0u;
-                        lo.z = (w[j].z << 4) & 0xF0F0F0F0u;
-                        lo.w = (w[j].w << 4) & 0xF0F0F0F0u;
-                        hi.x = w[j].x & 0xF0F0F0F0u;
-                        hi.y = w[j].y & 0xF0F0F0F0u;
-                        hi.z = w[j].z & 0xF0F0F0F0u;
-                        hi.w = w[j].w & 0xF0F0F0F0u;
-                        sts128(d, lo);
-                        sts128(d ^ 16u, hi);
+                        convert_chunk_to_smem(dst, i >> 2, i & 3, w[j]);
                     }
                 }
                 fence_proxy_async_smem();
@@ -451,39 +415,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// Packed matrix [rows][kbytes] of bytes; box = 64 bytes x box_rows, no swizzle, zero fill outside.
-int make_tmap(CUtensorMap *map, const void *base, int rows, int64_t kbytes, int box_rows)
-{
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point");
-    cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kbytes};
-    cuuint32_t box[2] = {(cuuint32_t)kPkRowBytes, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-    return QM_OK;
-}
-
 template <int BN, bool SWAP, int G>
 int prepare_one()
 {
@@ -504,9 +435,9 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *sc
     const int rowsQ = SWAP ? g.m : g.n;
     const int64_t kbytes = g.k / 2;
     CUtensorMap tmP, tmQ;
-    int st = make_tmap(&tmP, P, rowsP, kbytes, Cfg::kRowsP);
+    int st = make_packed_tmap(&tmP, P, rowsP, kbytes, Cfg::kRowsP, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (st != QM_OK) return st;
-    st = make_tmap(&tmQ, Q, rowsQ, kbytes, Cfg::kRowsQ);
+    st = make_packed_tmap(&tmQ, Q, rowsQ, kbytes, Cfg::kRowsQ, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (st != QM_OK) return st;
 
     const int tilesP = (rowsP + 128 * G - 1) / (128 * G);

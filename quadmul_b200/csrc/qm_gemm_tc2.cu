@@ -31,6 +31,7 @@
 #include "qm_epilogue.cuh"
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
+#include "qm_tc_common.cuh"
 
 // Optional per-role cycle accounting (compiled in only with -DQM_TC2_PROFILE): each role adds the
 // cycles between consecutive PROF marks to a slot; block 0 dumps them to g_tc2_prof at exit.
@@ -59,6 +60,7 @@ namespace qm {
 namespace {
 
 using namespace ptx;
+using namespace tc;
 
 constexpr int kBN = 256;         // UMMA N of the pair tile
 constexpr int kRowsA = 128;      // A rows per CTA
@@ -84,7 +86,6 @@ constexpr int kArrivals = kNumAConvWarps + kNumBConvWarps;  // converter warps p
 constexpr int kEpiBufBytes = kTmaStoreBufBytes;  // per epilogue warp: one 4 KB TMA-store buffer (or the 16-column fallback transposer)
 constexpr int kEpiBytes = kNumEpiWarps * kEpiBufBytes;
 static_assert(kEpiBufBytes >= EpilogueStage<16>::kBytesPerWarp, "epilogue buffer");
-constexpr int kRasterGroup = 8;
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 static_assert(kBItemsSub % kBConvThreads == 0, "B items");
 
@@ -100,28 +101,6 @@ struct Tc2Cfg {
     static_assert(kAccCols + S * kAStageCols <= kTmemCols, "TMEM budget");
     static_assert(kSmemBytes <= 232448, "shared memory");
 };
-
-__device__ __forceinline__ void tile_coords2(int t, int tilesP, int tilesQ, int &tp, int &tq)
-{
-    const int per_group = kRasterGroup * tilesQ;
-    const int g = t / per_group, rem = t - g * per_group;
-    const int p0 = g * kRasterGroup;
-    const int gsz = min(kRasterGroup, tilesP - p0);
-    tq = rem / gsz;
-    tp = p0 + (rem - tq * gsz);
-}
-
-__device__ __forceinline__ void report_timeout2(int *status, int site)
-{
-    if (atomicCAS(status, 0, (int)QM_ERR_TIMEOUT) == 0) status[1] = site | ((int)blockIdx.x << 8);
-}
-
-__device__ __forceinline__ uint64_t make_smem_desc2(uint32_t addr)
-{
-    const uint32_t lo = ((addr & 0x3FFFFu) >> 4) | (1u << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
-}
 
 // D[tmem] (+)= A[tmem] * B[smem desc], CTA pair, int8 -> int32.  One thread of the leader CTA.
 __device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
@@ -237,14 +216,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
-                tile_coords2(t / split_k, tilesP, tilesQ, tp, tq);
+                tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
                 const int yA = tp * 256 + (int)cta_rank * kRowsA;
                 const int yB = tq * kBN + (int)cta_rank * kRowsB;
                 for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                     const int s = it % SP;
                     const uint32_t ph = (it / SP) & 1u;
                     if (!mbar_wait(pk_empty(s), ph ^ 1u, abort_flag)) {
-                        report_timeout2(status, kWaitProducerSlot);
+                        report_timeout(status, kWaitProducerSlot);
                         *abort_flag = 1;
                         ok = false;
                         break;
@@ -273,7 +252,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             for (int t = unit; t < num_tiles && ok; t += num_units, ++lt) {
                 PROF(3)
                 if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag)) {
-                    report_timeout2(status, kWaitMmaAcc);
+                    report_timeout(status, kWaitMmaAcc);
                     *abort_flag = 1;
                     break;
                 }
@@ -284,7 +263,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
                     if (!mbar_wait(cv_full(s), ph, abort_flag)) {
-                        report_timeout2(status, kWaitMmaOperands);
+                        report_timeout(status, kWaitMmaOperands);
                         *abort_flag = 1;
                         ok = false;
                         break;
@@ -293,7 +272,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     tc_fence_after_sync();
 #pragma unroll
                     for (int h = 0; h < H; ++h) {
-                        const uint64_t dB = make_smem_desc2(cv0 + s * Cfg::kCvStage + h * kCvSub);
+                        const uint64_t dB = make_smem_desc(cv0 + s * Cfg::kCvStage + h * kCvSub);
                         const uint32_t ta = tmem_a0 + (uint32_t)(s * Cfg::kAStageCols + h * kASubCols);
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4)
@@ -333,13 +312,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         PROF_DECL
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
-            tile_coords2(t / split_k, tilesP, tilesQ, tp, tq);
+            tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
             PROF(2)
             const bool ok = warp_wait<false>(acc_full, lt & 1u, abort_flag, lane);
             PROF(0)
             if (!ok) {
                 if (lane == 0) {
-                    report_timeout2(status, kWaitEpilogueAcc);
+                    report_timeout(status, kWaitEpilogueAcc);
                     *abort_flag = 1;
                 }
                 break;
@@ -402,7 +381,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
-                        report_timeout2(status, kWaitConvertPacked);
+                        report_timeout(status, kWaitConvertPacked);
                         *abort_flag = 1;
                     }
                     ok = false;
@@ -420,7 +399,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
-                        report_timeout2(status, kWaitConvertSlot);
+                        report_timeout(status, kWaitConvertSlot);
                         *abort_flag = 1;
                     }
                     ok = false;
@@ -434,14 +413,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     uint32_t v[32];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        v[8 * c + 0] = (w[h][c].x << 4) & 0xF0F0F0F0u;
-                        v[8 * c + 1] = (w[h][c].y << 4) & 0xF0F0F0F0u;
-                        v[8 * c + 2] = (w[h][c].z << 4) & 0xF0F0F0F0u;
-                        v[8 * c + 3] = (w[h][c].w << 4) & 0xF0F0F0F0u;
-                        v[8 * c + 4] = w[h][c].x & 0xF0F0F0F0u;
-                        v[8 * c + 5] = w[h][c].y & 0xF0F0F0F0u;
-                        v[8 * c + 6] = w[h][c].z & 0xF0F0F0F0u;
-                        v[8 * c + 7] = w[h][c].w & 0xF0F0F0F0u;
+                        uint4 lo, hi;
+                        split_s4x32(w[h][c], lo, hi);
+                        v[8 * c + 0] = lo.x, v[8 * c + 1] = lo.y, v[8 * c + 2] = lo.z, v[8 * c + 3] = lo.w;
+                        v[8 * c + 4] = hi.x, v[8 * c + 5] = hi.y, v[8 * c + 6] = hi.z, v[8 * c + 7] = hi.w;
                     }
                     tmem_st_x32(ta + h * kASubCols, v);
                 }
@@ -466,7 +441,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
-                        report_timeout2(status, kWaitConvertPacked);
+                        report_timeout(status, kWaitConvertPacked);
                         *abort_flag = 1;
                     }
                     ok = false;
@@ -484,7 +459,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
-                        report_timeout2(status, kWaitConvertSlot);
+                        report_timeout(status, kWaitConvertSlot);
                         *abort_flag = 1;
                     }
                     ok = false;
@@ -498,19 +473,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < kBItersSub; ++j) {
                         const int i = j * kBConvThreads + ctid;
-                        const int rr = i >> 2, c = i & 3;
-                        const uint32_t d = dst + h * kCvSub + rr * kCvRowBytes + (((2 * c) ^ (rr & 7)) << 4);
-                        uint4 lo, hi;
-                        lo.x = (w[h][j].x << 4) & 0xF0F0F0F0u;
-                        lo.y = (w[h][j].y << 4) & 0xF0F0F0F0u;
-                        lo.z = (w[h][j].z << 4) & 0xF0F0F0F0u;
-                        lo.w = (w[h][j].w << 4) & 0xF0F0F0F0u;
-                        hi.x = w[h][j].x & 0xF0F0F0F0u;
-                        hi.y = w[h][j].y & 0xF0F0F0F0u;
-                        hi.z = w[h][j].z & 0xF0F0F0F0u;
-                        hi.w = w[h][j].w & 0xF0F0F0F0u;
-                        sts128(d, lo);
-                        sts128(d ^ 16u, hi);
+                        convert_chunk_to_smem(dst + h * kCvSub, i >> 2, i & 3, w[h][j]);
                     }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -532,63 +495,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     }
 }
 
-typedef CUresult (*EncodeTiledFn2)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn2 encode_fn2()
-{
-    static EncodeTiledFn2 fn = []() -> EncodeTiledFn2 {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn2>(p);
-    }();
-    return fn;
-}
-
-int make_tmap2(CUtensorMap *map, const void *base, int rows, int64_t kbytes, int box_rows, CUtensorMapSwizzle swizzle)
-{
-    EncodeTiledFn2 fn = encode_fn2();
-    if (!fn) return record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point");
-    cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kbytes};
-    cuuint32_t box[2] = {(cuuint32_t)kPkRowBytes, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-    return QM_OK;
-}
-
-// C as a 2-D int32 tensor [M][N] with row pitch ldc; 32 x 32 boxes, 128-byte swizzle.
-int make_tmap_c(CUtensorMap *map, const int32_t *C, int m, int n, int64_t ldc)
-{
-    EncodeTiledFn2 fn = encode_fn2();
-    if (!fn) return record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point");
-    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
-    cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
-    cuuint32_t box[2] = {32, 32};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(C), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(C)");
-    return QM_OK;
-}
-
 template <int H, bool MC>
 int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
     auto kernel = gemm_tc2_kernel<H, MC>;
     const int64_t kbytes = g.k / 2;
     CUtensorMap tmA, tmB;
-    int st = make_tmap2(&tmA, g.A, g.m, kbytes, kRowsA, CU_TENSOR_MAP_SWIZZLE_64B);
+    int st = make_packed_tmap(&tmA, g.A, g.m, kbytes, kRowsA, CU_TENSOR_MAP_SWIZZLE_64B);
     if (st != QM_OK) return st;
-    st = make_tmap2(&tmB, g.B, g.n, kbytes, kRowsB, CU_TENSOR_MAP_SWIZZLE_NONE);
+    st = make_packed_tmap(&tmB, g.B, g.n, kbytes, kRowsB, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (st != QM_OK) return st;
     const int num_kb = (g.k + H * kSubK - 1) / (H * kSubK);
     if (split_k < 1 || split_k > num_kb) return QM_ERR_ARG;
@@ -600,7 +515,7 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
         (allow_tma_store && !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && g.ldc < (1ll << 36)) ? 1 : 0;
     CUtensorMap tmC = tmA;  // placeholder when unused
     if (use_tma_store) {
-        st = make_tmap_c(&tmC, g.C, g.m, g.n, g.ldc);
+        st = make_c_tmap(&tmC, g.C, g.m, g.n, g.ldc);
         if (st != QM_OK) return st;
     }
     if (split_k > 1) {

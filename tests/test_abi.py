@@ -86,6 +86,30 @@ def test_plan(qm):
         qm.plan(4, 4, 3)
 
 
+def test_plan_is_consistent_over_a_grid_of_shapes(qm):
+    """Every plan the table produces must be launchable: known tile widths, K partitions no more than K blocks,
+    the pair tile only at 256 columns, decode tiles wide enough for m."""
+    from quadmul_b200 import _lib
+
+    for m in (1, 7, 16, 17, 33, 64, 65, 100, 128, 129, 300, 1024, 5000):
+        for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
+            for k in (32, 128, 512, 4096, 28672):
+                p = qm.plan(m, n, k)
+                assert p["kernel"] == _lib.QM_KERNEL_TC
+                assert p["tile_n"] in (16, 32, 64, 128, 256)
+                swap, pair, tm = p["swap_ab"] == 2, p["cta_pair"] == 2, p["a_tmem"] == 2
+                blocks = (k + 255) // 256 if tm else (k + 127) // 128
+                assert 1 <= p["split_k"] <= max(1, blocks)
+                if swap:
+                    assert m <= 64 and p["tile_n"] >= m and not pair and not tm
+                if tm:
+                    assert pair and p["tile_n"] == 256 and not swap
+                if pair:
+                    assert p["tile_n"] in (128, 256)
+                if not tm:
+                    assert p["split_k"] == 1 or swap
+
+
 def test_python_mirror_checks_arguments(qm):
     import torch
 
