@@ -113,6 +113,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(smem_raw + (tmem_slot - raw_u32));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_raw + (tmem_slot + 4 - raw_u32));
 
+    // Decode-sized launches are dominated by fixed costs, so they chain: the next launch in the stream may start
+    // its own set-up (barriers, TMEM, tensor-map fetch) while this one still runs, and touches global memory only
+    // after grid_dependency_wait() below.
+    if constexpr (SWAP) grid_launch_dependents();
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
     const int unit = (G == 2) ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // CTA or CTA pair
@@ -159,6 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    if constexpr (SWAP) grid_dependency_wait();  // everything before this line touched no global memory
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -455,7 +461,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *sc
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
     cfg.numAttrs = 0;
     if (G == 2) {
@@ -464,6 +470,13 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *sc
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.numAttrs = 1;
+    }
+    static const bool allow_pdl = !std::getenv("QM_NO_PDL");
+    if (SWAP && allow_pdl) {
+        // may begin while the previous kernel of the stream drains; the kernel itself waits before global accesses
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
     }
     // The tile list is static, so every CTA (pair) of the grid must be resident at once: a pair that
     // only starts when another has finished would run its whole share of tiles alone.

@@ -303,6 +303,20 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// launch_dependents: the next kernel in the stream (if it was launched with programmatic stream serialisation)
+// may start once every CTA of this grid has executed this or exited.  wait: blocks until the grids this one
+// depends on have completed and their memory is visible; returns at once when there is no such dependency.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
     uint32_t r;
