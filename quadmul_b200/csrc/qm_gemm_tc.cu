@@ -67,8 +67,14 @@ struct TcCfg {
     static constexpr int kRowsP = 128;     // rows of the UMMA-M operand held by this CTA
     static constexpr int kRowsQ = BN / G;  // rows of the UMMA-N operand held by this CTA
     static constexpr int kRows = kRowsP + kRowsQ;
-    static constexpr int kPkStage = kRows * kPkRowBytes;
-    static constexpr int kCvStage = kRows * kCvRowBytes;
+    // A pipeline stage holds H sub-blocks of 128 K-elements.  The decode form pays a fixed hand-off chain per stage
+    // (converter arrive, one thread issuing the MMAs and the commit), so it takes two sub-blocks per stage; the
+    // wide tiles keep one (their stages already fill the shared memory).
+    static constexpr int H = SWAP ? 2 : 1;
+    static constexpr int kPkSub = kRows * kPkRowBytes;
+    static constexpr int kCvSub = kRows * kCvRowBytes;
+    static constexpr int kPkStage = H * kPkSub;
+    static constexpr int kCvStage = H * kCvSub;
     static constexpr int SC = (3 * kCvStage + 4 * kPkStage <= kStageBudget) ? 3 : 2;
     static constexpr int SP_raw = (kStageBudget - SC * kCvStage) / kPkStage;
     static constexpr int SP = SP_raw > 8 ? 8 : SP_raw;
@@ -125,7 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 
     const int tilesP = (rowsP + 128 * G - 1) / (128 * G);
     const int tilesQ = (rowsQ + BN - 1) / BN;
-    const int num_kb_total = (K + kKBlock - 1) / kKBlock;
+    const int num_kb_total = (K + Cfg::H * kKBlock - 1) / (Cfg::H * kKBlock);  // stages; TMA zero-fills beyond K
     // A work item is one K partition of one output tile; partitions of a tile are adjacent items.
     const int num_tiles = tilesP * tilesQ * split_k;
     auto kb_begin = [&](int item) { return (int)(((long long)(item % split_k) * num_kb_total) / split_k); };
@@ -187,8 +193,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                     }
                     const uint32_t dst = pk0 + s * Cfg::kPkStage;
                     mbar_arrive_expect_tx(pk_full(s), Cfg::kPkStage);
-                    tma_load_2d(dst, &tmapP, kb * kPkRowBytes, yP, pk_full(s));
-                    tma_load_2d(dst + Cfg::kRowsP * kPkRowBytes, &tmapQ, kb * kPkRowBytes, yQ, pk_full(s));
+#pragma unroll
+                    for (int h = 0; h < Cfg::H; ++h) {
+                        const int x = (kb * Cfg::H + h) * kPkRowBytes;
+                        tma_load_2d(dst + h * Cfg::kPkSub, &tmapP, x, yP, pk_full(s));
+                        tma_load_2d(dst + h * Cfg::kPkSub + Cfg::kRowsP * kPkRowBytes, &tmapQ, x, yQ, pk_full(s));
+                    }
                 }
             }
         }
@@ -220,13 +230,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t stage = cv0 + s * Cfg::kCvStage;
-                    const uint64_t dP = make_smem_desc(stage);
-                    const uint64_t dQ = make_smem_desc(stage + Cfg::kRowsP * kCvRowBytes);
 #pragma unroll
-                    for (int k4 = 0; k4 < kKBlock / 32; ++k4) {
-                        // +32 bytes of K inside the 128-byte swizzled row = +2 in the address field
-                        umma_i8<G>(tmem_d, dP + 2u * k4, dQ + 2u * k4, Cfg::kIdesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                    for (int h = 0; h < Cfg::H; ++h) {
+                        const uint32_t sub = cv0 + s * Cfg::kCvStage + h * Cfg::kCvSub;
+                        const uint64_t dP = make_smem_desc(sub);
+                        const uint64_t dQ = make_smem_desc(sub + Cfg::kRowsP * kCvRowBytes);
+#pragma unroll
+                        for (int k4 = 0; k4 < kKBlock / 32; ++k4) {
+                            // +32 bytes of K inside the 128-byte swizzled row = +2 in the address field
+                            umma_i8<G>(tmem_d, dP + 2u * k4, dQ + 2u * k4, Cfg::kIdesc,
+                                       (kb != kb0 || (h | k4) != 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit<G>(cv_empty(s));
                     if constexpr (G == 2) umma_commit<G>(mapa_cluster(cv_empty(s), 1));
@@ -378,19 +392,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t src = pk0 + ps * Cfg::kPkStage;
-                const uint32_t dst = cv0 + cs * Cfg::kCvStage;
-                uint4 w[Cfg::kItemIters];
 #pragma unroll
-                for (int j = 0; j < Cfg::kItemIters; ++j) {
-                    const int i = j * kConvThreads + ctid;
-                    if (Cfg::kItems % kConvThreads == 0 || i < Cfg::kItems) w[j] = lds128(src + i * 16);
-                }
+                for (int h = 0; h < Cfg::H; ++h) {
+                    const uint32_t src = pk0 + ps * Cfg::kPkStage + h * Cfg::kPkSub;
+                    const uint32_t dst = cv0 + cs * Cfg::kCvStage + h * Cfg::kCvSub;
+                    uint4 w[Cfg::kItemIters];
 #pragma unroll
-                for (int j = 0; j < Cfg::kItemIters; ++j) {
-                    const int i = j * kConvThreads + ctid;
-                    if (Cfg::kItems % kConvThreads == 0 || i < Cfg::kItems) {
-                        convert_chunk_to_smem(dst, i >> 2, i & 3, w[j]);
+                    for (int j = 0; j < Cfg::kItemIters; ++j) {
+                        const int i = j * kConvThreads + ctid;
+                        if (Cfg::kItems % kConvThreads == 0 || i < Cfg::kItems) w[j] = lds128(src + i * 16);
+                    }
+#pragma unroll
+                    for (int j = 0; j < Cfg::kItemIters; ++j) {
+                        const int i = j * kConvThreads + ctid;
+                        if (Cfg::kItems % kConvThreads == 0 || i < Cfg::kItems) convert_chunk_to_smem(dst, i >> 2, i & 3, w[j]);
                     }
                 }
                 fence_proxy_async_smem();
@@ -448,7 +463,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *sc
 
     const int tilesP = (rowsP + 128 * G - 1) / (128 * G);
     const int tilesQ = (rowsQ + BN - 1) / BN;
-    const int num_kb = (g.k + kKBlock - 1) / kKBlock;
+    const int num_kb = (g.k + Cfg::H * kKBlock - 1) / (Cfg::H * kKBlock);  // stages
     if (split_k < 1 || split_k > num_kb || (split_k > 1 && G != 1)) return QM_ERR_ARG;
     const int64_t tiles = (int64_t)tilesP * tilesQ * split_k;
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
