@@ -558,7 +558,9 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 
 }  // namespace
 
-#define QM_TC2_FOR_EACH(X) X(1, false) X(2, false) X(1, true) X(2, true)
+// Built variants (sub-blocks per stage, pair-wide commit).  Measured at 8192^3 on B200 before the TMA-store epilogue:
+// (1, false) 442 us, (1, true) 418 us, (2, false) 337 us, (2, true) 328 us; only the fastest is compiled in.
+#define QM_TC2_FOR_EACH(X) X(2, true)
 
 int tc2_prepare_device()
 {
@@ -571,9 +573,6 @@ int tc2_prepare_device()
     return QM_OK;
 }
 
-// Variant: sub-blocks per stage (1 or 2) and one pair-wide commit (1) or two single commits (0).
-// Measured at 8192^3 on B200: "10" 442 us, "11" 418 us, "20" 337 us, "21" 328 us (before the TMA-store
-// epilogue; 303 us with it), so "21" is the default.  The environment variable QM_TC2_VARIANT overrides it.
 bool tc2_can_split(const GemmArgs &g)
 {
     return !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && !std::getenv("QM_NO_TMA_STORE");
@@ -581,15 +580,7 @@ bool tc2_can_split(const GemmArgs &g)
 
 int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
-    static const int variant = []() {
-        const char *e = std::getenv("QM_TC2_VARIANT");
-        return (e && (e[0] == '1' || e[0] == '2') && (e[1] == '0' || e[1] == '1')) ? (e[0] - '0') * 10 + (e[1] - '0') : 21;
-    }();
-#define X(H, MC) \
-    if (variant == H * 10 + (MC ? 1 : 0)) return tc2_launch_variant<H, MC>(g, ctx, split_k);
-    QM_TC2_FOR_EACH(X)
-#undef X
-    return QM_ERR_ARG;
+    return tc2_launch_variant<2, true>(g, ctx, split_k);
 }
 
 #ifdef QM_TC2_PROFILE
