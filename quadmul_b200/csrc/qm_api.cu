@@ -57,11 +57,15 @@ int ensure_ctx(DeviceCtx **out)
             }
             // split-K scratch: partial tiles and self-resetting arrival counters (zero between launches)
             void *scratch = nullptr, *counters = nullptr;
-            if ((e = cudaMalloc(&scratch, kScratchBytes)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(scratch)");
-            if ((e = cudaMalloc(&counters, kNumCounters * sizeof(int))) != cudaSuccess)
-                return record_cuda_error(e, "cudaMalloc(counters)");
-            if ((e = cudaMemset(counters, 0, kNumCounters * sizeof(int))) != cudaSuccess)
-                return record_cuda_error(e, "cudaMemset(counters)");
+            if ((e = cudaMalloc(&scratch, kScratchBytes)) == cudaSuccess &&
+                (e = cudaMalloc(&counters, kNumCounters * sizeof(int))) == cudaSuccess)
+                e = cudaMemset(counters, 0, kNumCounters * sizeof(int));
+            if (e != cudaSuccess) {
+                cudaFree(status);
+                cudaFree(scratch);
+                cudaFree(counters);
+                return record_cuda_error(e, "cudaMalloc/cudaMemset(split-K scratch)");
+            }
             c.scratch = static_cast<int32_t *>(scratch);
             c.scratch_bytes = kScratchBytes;
             c.counters = static_cast<int *>(counters);
