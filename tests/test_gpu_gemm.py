@@ -274,6 +274,49 @@ def test_cuda_graph_capture(qm, cuda_clean, oracle):
     assert np.array_equal(c.cpu().numpy(), oracle.gemm(ap, bp))
 
 
+def test_cuda_graph_capture_of_split_forms(qm, cuda_clean, oracle):
+    """The table's K-split forms inside a captured graph: pair tile + memset + TMA reduce-add, and the decode
+    form through scratch, replayed several times (counters and the zeroing must be part of every replay)."""
+    torch = cuda_clean
+    qm.init()
+    for m, n, k in [(128, 4096, 4096), (16, 4096, 4096)]:
+        assert qm.plan(m, n, k)["split_k"] > 1
+        ap = oracle.fill_packed(m, k, 81); bp = oracle.fill_packed(n, k, 82)
+        a, b = to_dev(torch, ap), to_dev(torch, bp)
+        c = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+        qm.gemm(a, b, c, m, n, k)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            qm.gemm(a, b, c, m, n, k)
+            qm.gemm(a, b, c, m, n, k)
+        want = oracle.gemm(ap, bp)
+        for _ in range(3):
+            c.fill_(12345)
+            g.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(c.cpu().numpy(), want)
+
+
+def test_two_streams_run_large_gemms_concurrently(qm, cuda_clean, oracle):
+    """The large-shape kernels keep no shared state between calls (no scratch): two streams may overlap."""
+    torch = cuda_clean
+    m, n, k = 1024, 2048, 1024
+    ops = []
+    for i in range(2):
+        ap = oracle.fill_packed(m, k, 90 + i); bp = oracle.fill_packed(n, k, 95 + i)
+        ops.append((to_dev(torch, ap), to_dev(torch, bp), torch.zeros((m, n), dtype=torch.int32, device="cuda"), oracle.gemm(ap, bp)))
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rep in range(4):
+        for (a, b, c, _), s in zip(ops, streams):
+            with torch.cuda.stream(s):
+                qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize()
+    for a, b, c, want in ops:
+        assert np.array_equal(c.cpu().numpy(), want)
+
+
 # ------------------------------------------------------------------ full-size configs
 def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     torch = cuda_clean

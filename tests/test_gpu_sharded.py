@@ -41,6 +41,26 @@ def test_shards_emulated_on_one_gpu(qm, cuda_clean, oracle, world, m, n, k):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
+def test_call_on_a_device_that_is_not_current(qm, cuda_clean, oracle):
+    """The reference launches on whichever device is current (extension.cpp:17-23 has no device guard); this mirror
+    switches to the operands' device for the call."""
+    torch = cuda_clean
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    m, n, k = 300, 520, 512
+    ap = oracle.fill_packed(m, k, 31); bp = oracle.fill_packed(n, k, 32)
+    a = torch.from_numpy(ap).view(torch.int8).to("cuda:1"); b = torch.from_numpy(bp).view(torch.int8).to("cuda:1")
+    c = torch.zeros((m, n), dtype=torch.int32, device="cuda:1")
+    assert torch.cuda.current_device() == 0
+    qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize(1)
+    assert torch.cuda.current_device() == 0
+    assert np.array_equal(c.cpu().numpy(), oracle.gemm(ap, bp))
+    with torch.cuda.device(1):
+        code, _ = qm.device_status()
+    assert code == 0
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
