@@ -37,6 +37,13 @@ __all__ = [
 
 _launches = 0  # kernels this package launched (one per call below; split-K adds none)
 
+# The compiled binding (csrc/torch_binding.cpp, built by `python -m quadmul_b200.build --torch`) shortens the host side
+# of gemm(); without it the same C-ABI entry point is reached through ctypes.  Either way the work is qm_gemm_s4.
+try:
+    from . import _quadmul_torch as _EXT  # noqa: F401
+except Exception:  # not built, or built against another torch
+    _EXT = None
+
 
 def launch_count() -> int:
     return _launches
@@ -90,6 +97,13 @@ def gemm(a, b, c, m: int, n: int, k: int) -> None:
     """C[m, n] (int32) = A[m, k] (s4) @ B[n, k]^T (s4) on packed operands; same call as the
     reference's quadmul.gemm (extension.cpp:8-24).  Asynchronous on the current stream."""
     global _launches
+    if _EXT is not None:
+        try:
+            _EXT.gemm(a, b, c, m, n, k)  # checks, device guard and status handling are in the binding
+        except RuntimeError as exc:
+            raise QuadmulError(-1, str(exc).split("\n")[0]) from exc
+        _launches += 1
+        return
     _check_gemm_tensors(a, b, c, m, n, k)
     with _on_device(a):
         st = LIB.qm_gemm_s4(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, _stream_of(a))

@@ -65,5 +65,43 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+TORCH_EXT_PATH = os.path.join(PKG_DIR, "_quadmul_torch.so")
+
+
+def build_torch_binding(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/torch_binding.cpp into quadmul_b200/_quadmul_torch.so (pybind11 + ATen; links the C-ABI library).
+
+    Optional: the package works through ctypes without it; the compiled binding only shortens the host-side path
+    of every call."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    src = os.path.join(CSRC, "torch_binding.cpp")
+    if not force and os.path.exists(TORCH_EXT_PATH) and os.path.getmtime(TORCH_EXT_PATH) >= max(
+            os.path.getmtime(src), os.path.getmtime(LIB_PATH)):
+        return TORCH_EXT_PATH
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    cuda_home = os.path.dirname(os.path.dirname(nvcc_path()))
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-w", "-DTORCH_EXTENSION_NAME=_quadmul_torch",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(cuda_home, "include")]:
+        cmd += ["-isystem", inc]
+    cmd += [src, "-o", TORCH_EXT_PATH, f"-L{PKG_DIR}", "-lquadmul_b200", "-Wl,-rpath,$ORIGIN"]
+    for lib in ce.library_paths():
+        cmd += [f"-L{lib}", f"-Wl,-rpath,{lib}"]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", f"-L{os.path.join(cuda_home, 'lib64')}",
+            "-lcudart"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed building _quadmul_torch.so")
+    return TORCH_EXT_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--torch" in sys.argv:
+        print(build_torch_binding(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
