@@ -374,7 +374,10 @@ def native_arm(args) -> None:
             achieved = per_launch_bytes / (avg_launch_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
         roofline.update({
-            "kernel": ("gemm_tc2_kernel<256x256 pair tile, A in TMEM>" if plan.get("a_tmem") == 2 else
+            "kernel": (f"gemm_dec_kernel<tile_n={plan['tile_n']}, B rows through TMEM, " +
+                       ("balanced shares" if plan.get("stream_k") == 2 else f"split_k={plan['split_k']}") + ">"
+                       if plan.get("a_tmem") == 2 and plan.get("swap_ab") == 2 else
+                       "gemm_tc2_kernel<256x256 pair tile, A in TMEM>" if plan.get("a_tmem") == 2 else
                        f"gemm_tc_kernel<tile_n={plan['tile_n']}, swap_ab={plan['swap_ab'] - 1}, cta_pair={plan['cta_pair']}>"),
             "traffic": DRAM_TRAFFIC_BYTES_PER_LAUNCH if not custom and not forced else None,
             "peak_note": peak_note,

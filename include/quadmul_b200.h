@@ -49,11 +49,13 @@ typedef struct qm_gemm_opts {
     int swap_ab;    /* 0 = table, 1 = C rows on UMMA-M (prefill form), 2 = C columns on UMMA-M  */
     int split_k;    /* 0 = table; >= 1 number of K partitions reduced through scratch memory    */
     int cta_pair;   /* 0 = table, 1 = single-CTA MMA, 2 = two-CTA (cta_group::2) MMA            */
-    int a_tmem;     /* 0 = table, 1 = operand A from shared memory, 2 = operand A from TMEM
-                       (only with tile_n 256, cta_pair 2, no swap, no split)                    */
+    int a_tmem;     /* 0 = table, 1 = the UMMA-M operand from shared memory, 2 = from TMEM: with tile_n 256,
+                       cta_pair 2 and no swap the large-shape kernel; with swap_ab 2 and tile_n 16/32/64
+                       the decode kernel                                                          */
     int plain_stores; /* 1 = write C with ordinary vector stores only (no TMA store); for a C that lives in
                          another GPU's memory (peer mapping), as the fused gather of the sharded driver uses */
-    int reserved[1];
+    int stream_k;   /* decode kernel only: 0 = table, 1 = K partitions per tile (split_k), 2 = one equal contiguous
+                       share of the (tile, K) work per SM, partial tiles summed through scratch memory */
 } qm_gemm_opts_t;
 
 const char *qm_status_string(int status);

@@ -27,7 +27,7 @@ class GemmOpts(ctypes.Structure):
         ("cta_pair", _i),
         ("a_tmem", _i),
         ("plain_stores", _i),
-        ("reserved", _i * 1),
+        ("stream_k", _i),
     ]
 
 

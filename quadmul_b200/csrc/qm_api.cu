@@ -51,6 +51,7 @@ int ensure_ctx(DeviceCtx **out)
             if ((e = cudaMemset(status, 0, 2 * sizeof(int))) != cudaSuccess) return record_cuda_error(e, "cudaMemset(status)");
             int st = tc_prepare_device();
             if (st == QM_OK) st = tc2_prepare_device();
+            if (st == QM_OK) st = dec_prepare_device();
             if (st != QM_OK) {
                 cudaFree(status);
                 return st;
@@ -128,18 +129,31 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->a_tmem < 0 || opts->a_tmem > 2) return QM_ERR_ARG;
         if (opts->a_tmem) p.a_tmem = opts->a_tmem - 1;
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair) p.a_tmem = 0;
+        if (opts->stream_k < 0 || opts->stream_k > 2) return QM_ERR_ARG;
+        if (opts->stream_k) p.stream_k = opts->stream_k - 1;
+        else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k) p.stream_k = 0;
+        if (p.stream_k && !(p.a_tmem && p.swap_ab)) return QM_ERR_ARG;  // only the decode kernel has it
+    }
+    if (p.split_k > 1 && !(opts && opts->split_k) && (p.swap_ab || !p.a_tmem) &&
+        (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
+        p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
+    if (p.a_tmem && p.swap_ab) {
+        if ((p.tile_n != 16 && p.tile_n != 32 && p.tile_n != 64) || p.cta_pair != 1) return QM_ERR_ARG;
+        st = dec_launch(g, p, *ctx);
+        if (st == QM_ERR_WORKSPACE && p.stream_k && !(opts && opts->stream_k)) {
+            p.stream_k = 0, p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
+            st = dec_launch(g, p, *ctx);
+        }
+        return st;
     }
     if (p.a_tmem) {
-        if (p.swap_ab || p.tile_n != 256 || p.cta_pair != 2) return QM_ERR_ARG;
+        if (p.tile_n != 256 || p.cta_pair != 2) return QM_ERR_ARG;
         if (p.split_k > 1 && !tc2_can_split(g)) {
             if (opts && opts->split_k) return QM_ERR_ALIGN;
             p.split_k = 1;
         }
         return tc2_launch(g, *ctx, p.split_k);
     }
-    if (p.split_k > 1 && !(opts && opts->split_k) &&
-        (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
-        p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
     return tc_launch(g, p, *ctx);
 }
 
@@ -366,6 +380,7 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
     opts->split_k = p.split_k;
     opts->cta_pair = p.cta_pair;
     opts->a_tmem = p.a_tmem + 1;
+    opts->stream_k = p.stream_k + 1;
     return QM_OK;
 }
 

@@ -50,7 +50,9 @@ struct TcPlan {
     int swap_ab;   // 0: C rows on UMMA-M; 1: C columns (B rows) on UMMA-M
     int split_k;   // >= 1
     int cta_pair;  // 1 or 2
-    int a_tmem;    // 1: the 256 x 256 pair tile with operand A in TMEM (gemm_tc2_kernel)
+    int a_tmem;    // 1: the UMMA-M operand goes through TMEM: gemm_tc2_kernel (256 x 256 pair tile) or, with swap_ab,
+                   //    gemm_dec_kernel (decode form)
+    int stream_k;  // 1 (gemm_dec_kernel only): one equal contiguous share of the (tile, K) work per SM instead of split_k
 };
 
 // qm_gemm_tc.cu
@@ -65,6 +67,10 @@ int tc_counters_needed(int m, int n, const TcPlan &p);
 int tc2_prepare_device();
 int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k);
 bool tc2_can_split(const GemmArgs &g);  // K partitions accumulate through TMA reduce-add: needs an aligned local C
+
+// qm_gemm_dec.cu: decode form (swap_ab, tile_n 16/32/64), B rows through TMEM; split-K through the context's scratch
+int dec_prepare_device();
+int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
 
 // qm_gemm_simt.cu
 int simt_launch(const GemmArgs &g);

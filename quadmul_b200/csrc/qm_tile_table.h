@@ -15,7 +15,10 @@ struct PlanRule {
 };
 
 // Ordered by m_max.  Decode-sized m (<= 64) puts the weights on the M axis so that a 128-row MMA is fully
-// used by weight rows and only `tile_n` (>= m) columns are spent on tokens.  Everything larger runs
+// used by weight rows and only `tile_n` (>= m) columns are spent on tokens; it runs gemm_dec_kernel, which
+// feeds the converted weights to the MMA from TMEM (measured against the all-shared-memory form of
+// gemm_tc_kernel: 16 x 11008 x 4096 11.6 vs 12.5 us, 64 x 4096 x 4096 13.0 vs 14.8 us, 64 x 11008 x 4096
+// 13.7 vs 15.5 us, equal at 16 x 4096 x 4096).  Everything larger runs
 // the 256 x 256 CTA-pair tile: measured on B200 it beats the single-CTA 128 x 256 and both 128-wide
 // forms at 8192^3 and at all four M = 2048 prefill shapes (python -m quadmul_b200.tune), because
 // each SM converts and feeds only half of the B tile.
@@ -34,7 +37,7 @@ inline bool tc_eligible(const GemmArgs &g)
 
 inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
-    TcPlan p{256, 0, 1, 1, 0};
+    TcPlan p{256, 0, 1, 1, 0, 0};
     for (const PlanRule &r : kPlanRules) {
         if (m <= r.m_max) {
             p.tile_n = r.tile_n;
@@ -52,6 +55,10 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
         if (s > 4) s = 4;
         if (s > num_kb / 2) s = num_kb / 2;
         p.split_k = s < 1 ? 1 : s;
+        p.a_tmem = 1;
+        // More tiles than SMs: whole tiles leave the last round partly empty (224 tiles on 148 SMs: 34.7 us),
+        // equal contiguous shares of the (tile, K) work do not (29.6 us; 16 x 57344 x 8192: 52 us = 4.6 TB/s).
+        if (tiles > num_sms) p.stream_k = 1, p.split_k = 1;
     }
     if (!p.swap_ab) {
         // narrow outputs: do not spend a 256-wide tile on fewer columns

@@ -26,6 +26,12 @@ def variants(m: int, n: int):
             if tn >= min(m, 128) or tn == 128:
                 for sk in ((1, 2, 3, 4, 6, 8, 16) if m <= 64 else (1, 2, 4)):
                     out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk))
+    if m <= 64:  # decode kernel: B rows through TMEM
+        for tn in (16, 32, 64):
+            if tn >= m:
+                for sk in (1, 2, 3, 4, 5, 6, 8):
+                    out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk, a_tmem=2))
+                out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, a_tmem=2, stream_k=2))
     if m > 64:
         for tn in (128, 256):
             out.append(dict(tile_n=tn, swap_ab=1, cta_pair=1, split_k=1))

@@ -79,7 +79,8 @@ def test_plan(qm):
     assert p["kernel"] == _lib.QM_KERNEL_TC and p["tile_n"] == 256 and p["swap_ab"] == 1 and p["cta_pair"] == 2 and p["a_tmem"] == 2
     assert qm.plan(128, 4096, 4096)["a_tmem"] == 2 and qm.plan(128, 4096, 4096)["split_k"] == 4
     d = qm.plan(16, 4096, 4096)
-    assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16
+    assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16 and d["a_tmem"] == 2
+    assert d["stream_k"] == 1 and qm.plan(16, 28672, 8192)["stream_k"] == 2  # more tiles than SMs: equal shares
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -101,9 +102,12 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
                 blocks = (k + 255) // 256 if tm else (k + 127) // 128
                 assert 1 <= p["split_k"] <= max(1, blocks)
                 if swap:
-                    assert m <= 64 and p["tile_n"] >= m and not pair and not tm
-                if tm:
-                    assert pair and p["tile_n"] == 256 and not swap
+                    assert m <= 64 and p["tile_n"] in (16, 32, 64) and p["tile_n"] >= m and not pair and tm
+                    assert p["stream_k"] == 1 or p["split_k"] == 1
+                else:
+                    assert p["stream_k"] == 1
+                if tm and not swap:
+                    assert pair and p["tile_n"] == 256
                 if pair:
                     assert p["tile_n"] in (128, 256)
                 if not tm:

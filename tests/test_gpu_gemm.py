@@ -99,6 +99,30 @@ def test_split_k_through_scratch(qm, cuda_clean, oracle, golden, split_k):
             run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **tc(64, 2, 1, split_k))
 
 
+@pytest.mark.parametrize("tile_n", [16, 32, 64])
+@pytest.mark.parametrize("split_k", [1, 2, 3, 4, 8, "balanced"])
+def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, tile_n, split_k):
+    """gemm_dec_kernel: B rows on UMMA-M, converted in registers and fed to the MMA from TMEM.  Ragged n, m above and
+    below the tile, a K tail inside a 256-element stage, several tiles per CTA, and twice in a row (arrival counters).
+    "balanced" cuts the (tile, K) work into one equal contiguous share per SM instead of K partitions per tile."""
+    if split_k == "balanced":
+        opts = dict(tc(tile_n, 2, 1, 0), a_tmem=2, stream_k=2)
+    else:
+        opts = dict(tc(tile_n, 2, 1, split_k), a_tmem=2)
+    cases = [(16, 1024, 4096), (1, 384, 2048), (64, 1280, 2048), (40, 200, 4096), (7, 130, 2080), (100, 5000, 2048)]
+    for m, n, k in cases:
+        ap = oracle.fill_packed(m, k, 61); bp = oracle.fill_packed(n, k, 62)
+        want = oracle.gemm(ap, bp)
+        for _ in range(2):
+            _check(qm, cuda_clean, oracle, ap, bp, want=want, **opts)
+    if split_k in (1, "balanced"):
+        for name, g in golden.items():
+            got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **opts)
+            assert np.array_equal(got, g["c"]), f"{name} tile_n={tile_n}: " + mismatch_report(got, g["c"])
+        ap = oracle.fill_packed(3, 32, 63); bp = oracle.fill_packed(129, 32, 64)  # one MMA slice of K
+        _check(qm, cuda_clean, oracle, ap, bp, **opts)
+
+
 # ------------------------------------------------------------------ seeded random shapes
 @pytest.mark.parametrize(
     "m,n,k",
