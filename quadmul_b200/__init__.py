@@ -112,15 +112,15 @@ def gemm(a, b, c, m: int, n: int, k: int) -> None:
 
 
 def gemm_ex(a, b, c, m: int, n: int, k: int, *, kernel: int = 0, tile_n: int = 0, swap_ab: int = 0, split_k: int = 0,
-            cta_pair: int = 0, a_tmem: int = 0, stream_k: int = 0) -> None:
+            cta_pair: int = 0, a_tmem: int = 0, stream_k: int = 0, ctas_per_sm: int = 0) -> None:
     """gemm with explicit kernel and tile choices (qm_gemm_s4_ex); for tuning and tests."""
     global _launches
     _check_gemm_tensors(a, b, c, m, n, k)
     opts = GemmOpts(kernel=kernel, tile_n=tile_n, swap_ab=swap_ab, split_k=split_k, cta_pair=cta_pair, a_tmem=a_tmem,
-                    stream_k=stream_k)
+                    stream_k=stream_k, ctas_per_sm=ctas_per_sm)
     with _on_device(a):
         st = LIB.qm_gemm_s4_ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, _stream_of(a), ctypes.byref(opts))
-    check(st, f"quadmul.gemm_ex(m={m}, n={n}, k={k}, tile_n={tile_n}, swap_ab={swap_ab}, split_k={split_k}, cta_pair={cta_pair}, a_tmem={a_tmem}, stream_k={stream_k})")
+    check(st, f"quadmul.gemm_ex(m={m}, n={n}, k={k}, tile_n={tile_n}, swap_ab={swap_ab}, split_k={split_k}, cta_pair={cta_pair}, a_tmem={a_tmem}, stream_k={stream_k}, ctas_per_sm={ctas_per_sm})")
     _launches += 1
 
 
@@ -195,7 +195,7 @@ def plan(m: int, n: int, k: int) -> dict:
     o = GemmOpts()
     check(LIB.qm_plan(m, n, k, ctypes.byref(o)), "plan")
     return {"kernel": o.kernel, "tile_n": o.tile_n, "swap_ab": o.swap_ab, "split_k": o.split_k, "cta_pair": o.cta_pair,
-            "a_tmem": o.a_tmem, "stream_k": o.stream_k}
+            "a_tmem": o.a_tmem, "stream_k": o.stream_k, "ctas_per_sm": o.ctas_per_sm}
 
 
 def device_status(clear: bool = True) -> tuple[int, int]:

@@ -28,6 +28,7 @@ class GemmOpts(ctypes.Structure):
         ("a_tmem", _i),
         ("plain_stores", _i),
         ("stream_k", _i),
+        ("ctas_per_sm", _i),
     ]
 
 

@@ -129,14 +129,20 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->a_tmem < 0 || opts->a_tmem > 2) return QM_ERR_ARG;
         if (opts->a_tmem) p.a_tmem = opts->a_tmem - 1;
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair) p.a_tmem = 0;
-        if (opts->stream_k < 0 || opts->stream_k > 2) return QM_ERR_ARG;
+        if (opts->stream_k < 0 || opts->stream_k > 3) return QM_ERR_ARG;
         if (opts->stream_k) p.stream_k = opts->stream_k - 1;
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k) p.stream_k = 0;
         if (p.stream_k && !(p.a_tmem && p.swap_ab)) return QM_ERR_ARG;  // only the decode kernel has it
+        if (opts->ctas_per_sm < 0 || opts->ctas_per_sm > 2) return QM_ERR_ARG;
+        if (opts->ctas_per_sm) p.ctas_per_sm = opts->ctas_per_sm;
+        else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k || opts->stream_k) p.ctas_per_sm = 1;
+        if (p.ctas_per_sm == 2 && !(p.a_tmem && p.swap_ab && p.tile_n == 16)) return QM_ERR_ARG;
     }
-    if (p.split_k > 1 && !(opts && opts->split_k) && (p.swap_ab || !p.a_tmem) &&
+    const bool through_scratch = (p.swap_ab || !p.a_tmem) && !(p.swap_ab && p.a_tmem && p.stream_k == 2);
+    if (p.split_k > 1 && !(opts && opts->split_k) && through_scratch &&
         (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
         p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
+    if (p.stream_k == 2 && p.split_k < 2) p.stream_k = 0;  // a cluster of one partition is the plain form
     if (p.a_tmem && p.swap_ab) {
         if ((p.tile_n != 16 && p.tile_n != 32 && p.tile_n != 64) || p.cta_pair != 1) return QM_ERR_ARG;
         st = dec_launch(g, p, *ctx);
@@ -198,7 +204,7 @@ const char *qm_status_string(int status)
     }
 }
 
-int qm_version(void) { return 100; }
+int qm_version(void) { return 101; }
 
 const char *qm_last_cuda_error(void) { return t_last_error.c_str(); }
 
@@ -381,6 +387,7 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
     opts->cta_pair = p.cta_pair;
     opts->a_tmem = p.a_tmem + 1;
     opts->stream_k = p.stream_k + 1;
+    opts->ctas_per_sm = p.ctas_per_sm;
     return QM_OK;
 }
 

@@ -22,9 +22,7 @@
 //    each column is one coalesced 128-byte store).  With K split over CTAs the partial tiles meet in
 //    scratch memory and whichever partition arrives last adds them up (no CTA waits for another).
 //
-// TMEM map (512 columns): two accumulator buffers of NA x BN columns (the K slices of a stage go round-robin
-// into NA partial accumulators so that consecutive MMAs do not depend on each other; the epilogue adds
-// them), then the operand ring of SC stages, 128 lanes x
+// TMEM map (512 / R columns): two accumulators of BN columns, then the operand ring of SC stages, 128 lanes x
 // 32 columns per sub-block (128 bytes of K per row: four 32-byte MMA slices, each 16 bytes of even
 // elements then 16 bytes of odd elements, the K order the A converters produce as well).
 //
@@ -79,34 +77,57 @@ constexpr int kNumWarps = kFirstQConvWarp + kNumQConvWarps;  // 16
 constexpr int kNumThreads = kNumWarps * 32;
 constexpr int kQConvThreads = kNumQConvWarps * 32;
 constexpr int kArrivals = kNumPConvWarps + kNumQConvWarps;
-constexpr int kStageBudget = 200 * 1024;
-constexpr int kTmemCols = 512;
-
-template <int BN>
+// R = CTAs of this kernel that fit on one SM at a time.  With R = 2 a CTA takes half of the shared memory, TMEM and
+// registers: two CTAs of one launch hide each other's pipeline bubbles, and under programmatic dependent launch the
+// next launch's CTAs are resident (set up, first weights requested) while this launch's CTAs are still working.
+//
+// CL = the K partitions of a tile form a thread-block cluster (one CTA each) and add their partial tiles up through
+// the cluster's shared memory instead of global scratch: partition r sends the 32-row quarters it does not own to their
+// owners with st.async (data + byte count on the owner's mbarrier) and sums the quarters it owns (quarter q belongs to
+// partition q % split_k).
+template <int BN, int R, bool CL>
 struct DecCfg {
     static_assert(BN == 16 || BN == 32 || BN == 64, "UMMA N of the decode form");
+    static_assert(R == 1 || R == 2, "CTAs per SM");
+    static_assert(!CL || R == 1, "the cluster form runs one CTA per SM");
+    static constexpr int kRxSlotBytes = 32 * BN * 4;              // one quarter of a partial tile, [row][BN] int32
+    static constexpr int kRxSlots = 4;                            // owned quarters x senders: at most 2 x 2 (split_k = 3)
+    static constexpr int kRxBytes = CL ? kRxSlots * kRxSlotBytes : 0;
+    static constexpr int kStageBudget = R == 1 ? 200 * 1024 : 104 * 1024;
+    static constexpr int kTmemCols = 512 / R;
     static constexpr int kPkSubQ = BN * kPkRowBytes;
     static constexpr int kCvSubQ = BN * 128;
     static constexpr int kPkStage = kH * (kPkSubP + kPkSubQ);
     static constexpr int kCvStage = kH * kCvSubQ;
-    // MMAs into one accumulator depend on each other, and at N = 16..64 an MMA is far shorter than the tensor
-    // pipe is deep: the K slices of a stage go round-robin into NA accumulators, which the epilogue adds up.
-    static constexpr int NA = BN <= 32 ? 4 : 2;
-    static constexpr int kAccBufCols = NA * BN;
-    static constexpr int kAccCols = 2 * kAccBufCols;
-    static constexpr int SC = BN == 16 ? 6 : 4;
-    static constexpr int SP_raw = (kStageBudget - SC * kCvStage) / kPkStage;
+    static constexpr int kAccCols = 2 * BN;  // two accumulators
+    static constexpr int SC = R == 1 ? (BN <= 32 ? 6 : 4) : (BN <= 32 ? 3 : 2);
+    static constexpr int SP_raw = (kStageBudget - SC * kCvStage - kRxBytes) / kPkStage;
     static constexpr int SP = SP_raw > 10 ? 10 : SP_raw;
-    static constexpr int kNumBarriers = 2 * SP + 2 * SC + 4;
-    static constexpr int kSmemBytes = 1024 + SC * kCvStage + SP * kPkStage + kNumBarriers * 8 + 16;
+    static constexpr int kNumBarriers = 2 * SP + 2 * SC + 4 + 2;  // ... + two receive barriers (owned quarters)
+    static constexpr int kSmemBytes = 1024 + SC * kCvStage + SP * kPkStage + kRxBytes + kNumBarriers * 8 + 16;
     static constexpr int kQItems = kH * BN * 4;  // 16-byte packed chunks of A per stage
     static constexpr int kQIters = kQItems / kQConvThreads;
     static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     static_assert(kAccCols + SC * kH * kASubCols <= kTmemCols, "TMEM budget");
-    static_assert(kSmemBytes <= 232448, "shared memory");
+    static_assert(R * (kSmemBytes + 1024) <= 232448, "shared memory");
+    static_assert(SP >= 2, "packed ring");
     static_assert(kPkStage % 1024 == 0 && kCvSubQ % 1024 == 0, "stage alignment");
     static_assert(kQItems % kQConvThreads == 0, "A items");
 };
+
+// 16 bytes into the shared memory of another CTA of the cluster; the bytes are counted on that CTA's mbarrier.
+__device__ __forceinline__ void st_async_v4(uint32_t remote_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t remote_bar)
+{
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(remote_addr),
+                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(remote_bar)
+                 : "memory");
+}
+
+// L2 prefetch of one TMA box: no shared memory, no barrier, no architectural effect.
+__device__ __forceinline__ void tma_prefetch_2d(const void *tmap, int32_t x, int32_t y)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 
 // D[tmem] (+)= A[tmem] * B[smem desc], int8 -> int32, one CTA.  One thread issues it.
 __device__ __forceinline__ void umma_i8_ta1(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
@@ -189,28 +210,30 @@ struct WorkList {
     }
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kNumThreads, 1)
+template <int BN, int R, bool CL>
+__global__ void __launch_bounds__(kNumThreads, R)
 gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
                 int32_t *__restrict__ C, int64_t ldc, int rowsP, int rowsQ, int K, int *status, int split_k, int parts_stride,
                 int32_t *__restrict__ scratch, int *__restrict__ counters)
 {
     // split_k >= 1: K partitions per tile (parts_stride = split_k); split_k == 0: balanced shares, at most parts_stride
     // pieces per tile.  Piece `part` of tile `tile` owns scratch slot tile * parts_stride + part.
-    using Cfg = DecCfg<BN>;
+    using Cfg = DecCfg<BN, R, CL>;
     constexpr int SP = Cfg::SP, SC = Cfg::SC;
     extern __shared__ uint8_t smem_raw[];
 
     const uint32_t raw_u32 = smem_u32(smem_raw);
     const uint32_t cv0 = (raw_u32 + 1023u) & ~1023u;  // converted A stages: [stage][sub-block][row][128 B]
     const uint32_t pk0 = cv0 + SC * Cfg::kCvStage;    // packed stages: [stage][B sub-blocks (swizzle 64B)][A sub-blocks (linear)]
-    const uint32_t bar0 = pk0 + SP * Cfg::kPkStage;
+    const uint32_t rx0 = pk0 + SP * Cfg::kPkStage;    // cluster form: received quarters of partial tiles
+    const uint32_t bar0 = rx0 + Cfg::kRxBytes;
     auto pk_full = [&](int s) { return bar0 + 8u * s; };
     auto pk_empty = [&](int s) { return bar0 + 8u * (SP + s); };
     auto cv_full = [&](int s) { return bar0 + 8u * (2 * SP + s); };
     auto cv_empty = [&](int s) { return bar0 + 8u * (2 * SP + SC + s); };
     auto acc_full = [&](int b) { return bar0 + 8u * (2 * SP + 2 * SC + b); };
     auto acc_empty = [&](int b) { return bar0 + 8u * (2 * SP + 2 * SC + 2 + b); };
+    auto rx_bar = [&](int qi) { return bar0 + 8u * (2 * SP + 2 * SC + 4 + qi); };
     const uint32_t tmem_slot = bar0 + 8u * Cfg::kNumBarriers;
     uint32_t *tmem_slot_ptr = reinterpret_cast<uint32_t *>(smem_raw + (tmem_slot - raw_u32));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_raw + (tmem_slot + 4 - raw_u32));
@@ -237,6 +260,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full(b), 1);
             mbar_init(acc_empty(b), 4);
+            mbar_init(rx_bar(b), 1);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -247,15 +271,35 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
         prefetch_tmap(&tmapQ);
     }
     if (warp == 1) {
-        tmem_alloc<1>(tmem_slot, kTmemCols);
+        tmem_alloc<1>(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish<1>();
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CL) {
+        // the peers' receive barriers must exist before anything is sent to them
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
     const uint32_t tmem_a0 = tmem_base + Cfg::kAccCols;
-    grid_dependency_wait();  // everything before this line touched no global memory
+    if (warp == 0 && lane == 0) {
+        // Ask L2 for the first ring-full of B before waiting for the previous kernel: a prefetch changes nothing
+        // the program can observe (L2 is the coherence point, so even a B the previous kernel still writes reads
+        // correctly afterwards), and the loads issued after the wait then find their lines on the way or in L2.
+        WorkList ahead = work;
+        Work wa;
+        int n = 0;
+        while (n < SP && ahead.next(wa)) {
+            const int yP = (wa.tile % tilesP) * kRowsP;
+            for (int kb = wa.kb0; kb < wa.kb1 && n < SP; ++kb, ++n) {
+#pragma unroll
+                for (int h = 0; h < kH; ++h) tma_prefetch_2d(&tmapP, (kb * kH + h) * kPkRowBytes, yP);
+            }
+        }
+    }
+    grid_dependency_wait();  // nothing before this line read or wrote global memory (the prefetch returns no data)
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -306,7 +350,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 }
                 PROF(0)
                 tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kAccBufCols);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 const int kb0 = w.kb0;
                 for (int kb = kb0; kb < w.kb1; ++kb, ++it) {
                     const int s = it % SC;
@@ -324,11 +368,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                         const uint64_t dQ = make_smem_desc(cv0 + s * Cfg::kCvStage + h * Cfg::kCvSubQ);
                         const uint32_t ta = tmem_a0 + (uint32_t)((s * kH + h) * kASubCols);
 #pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4) {
-                            const int slice = h * 4 + k4;
-                            umma_i8_ta1(tmem_d + (uint32_t)((slice % Cfg::NA) * BN), ta + 8u * k4, dQ + 2u * k4, Cfg::kIdesc,
-                                        (kb != kb0 || slice >= Cfg::NA) ? 1u : 0u);
-                        }
+                        for (int k4 = 0; k4 < 4; ++k4)
+                            umma_i8_ta1(tmem_d, ta + 8u * k4, dQ + 2u * k4, Cfg::kIdesc, (kb != kb0 || (h | k4) != 0) ? 1u : 0u);
                     }
                     umma_commit<1>(cv_empty(s));
                     PROF(2)
@@ -357,43 +398,90 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
             }
             PROF(0)
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * Cfg::kAccBufCols);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
             const int row = quarter * 32 + lane;
             const int p = (tile % tilesP) * kRowsP + row;  // row of B = column of C
             const int q0 = (tile / tilesP) * BN;           // first row of A = row of C
-            uint32_t v[BN];
+            if constexpr (CL) {
+                if (w.nparts > 1) {
+                    // One piece per CTA, cluster rank = piece.  Row = lane, BN int32 per row, 16-byte chunks XOR-swizzled
+                    // so that the owner's 16-byte reads do not collide on banks.
+                    constexpr int kChunks = BN / 4;
+                    const uint32_t swz = BN == 16 ? (uint32_t)((lane >> 1) & 3) : (uint32_t)(lane & 7);
+                    uint32_t v[BN];
 #pragma unroll
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t part[Cfg::NA][16];
+                    for (int c = 0; c < BN; c += 16) tmem_ld_x16(taddr + c, *reinterpret_cast<uint32_t(*)[16]>(&v[c]));
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty(buf));
+                    PROF(1)
+                    const int owner = quarter % w.nparts, qi = quarter / w.nparts;
+                    if (owner != w.part) {
+                        const int sender = w.part < owner ? w.part : w.part - 1;
+                        const uint32_t slot = rx0 + (uint32_t)((qi * (w.nparts - 1) + sender) * Cfg::kRxSlotBytes) + (uint32_t)lane * (BN * 4);
+                        const uint32_t rslot = mapa_cluster(slot, (uint32_t)owner);
+                        const uint32_t rbar = mapa_cluster(rx_bar(qi), (uint32_t)owner);
 #pragma unroll
-                for (int a = 0; a < Cfg::NA; ++a) tmem_ld_x16(taddr + a * BN + c, part[a]);
-                tmem_ld_wait();
+                        for (int c = 0; c < kChunks; ++c)
+                            st_async_v4(rslot + (((uint32_t)c ^ swz) << 4), (uint32_t)((int32_t)v[4 * c] >> 8), (uint32_t)((int32_t)v[4 * c + 1] >> 8),
+                                        (uint32_t)((int32_t)v[4 * c + 2] >> 8), (uint32_t)((int32_t)v[4 * c + 3] >> 8), rbar);
+                    } else {
+                        if (lane == 0) mbar_arrive_expect_tx(rx_bar(qi), (uint32_t)((w.nparts - 1) * Cfg::kRxSlotBytes));
+                        __syncwarp();
+                        if (!warp_wait<false>(rx_bar(qi), 0u, abort_flag, lane)) {
+                            if (lane == 0) {
+                                report_timeout(status, kWaitSplitK);
+                                *abort_flag = 1;
+                            }
+                            break;
+                        }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    uint32_t sum = part[0][j];
+                        for (int j = 0; j < BN; ++j) v[j] = (uint32_t)((int32_t)v[j] >> 8);
+                        for (int sdr = 0; sdr < w.nparts - 1; ++sdr) {
+                            const uint32_t slot = rx0 + (uint32_t)((qi * (w.nparts - 1) + sdr) * Cfg::kRxSlotBytes) + (uint32_t)lane * (BN * 4);
 #pragma unroll
-                    for (int a = 1; a < Cfg::NA; ++a) sum += part[a][j];
-                    v[c + j] = sum;
+                            for (int c = 0; c < kChunks; ++c) {
+                                const uint4 x = lds128(slot + (((uint32_t)c ^ swz) << 4));
+                                v[4 * c] += x.x, v[4 * c + 1] += x.y, v[4 * c + 2] += x.z, v[4 * c + 3] += x.w;
+                            }
+                        }
+                        if (p < rowsP) {
+#pragma unroll
+                            for (int j = 0; j < BN; ++j)
+                                if (q0 + j < rowsQ) C[(int64_t)(q0 + j) * ldc + p] = (int32_t)v[j];
+                        }
+                    }
+                    continue;
                 }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(buf));  // the accumulator is in registers
-            PROF(1)
-            if (w.nparts == 1) {
-                if (p < rowsP) {
-#pragma unroll
-                    for (int j = 0; j < BN; ++j)
-                        if (q0 + j < rowsQ) C[(int64_t)(q0 + j) * ldc + p] = (int32_t)v[j] >> 8;
-                }
-                continue;
-            }
-            // Partial tile -> scratch as [column][row] (coalesced); whichever piece of the tile finishes last sums all
-            // of them.  Each warp owns 32 rows of the tile and its own arrival counter: nobody waits.
+            // Partial tiles go to scratch as [column][row] (coalesced); whichever piece of the tile finishes last
+            // sums all of them.  Each warp owns 32 rows of the tile and its own arrival counter: nobody waits.
             int32_t *parts = scratch + (int64_t)tile * parts_stride * (kRowsP * BN);
             int32_t *mine = parts + (int64_t)w.part * (kRowsP * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t v[16];
+                tmem_ld_x16(taddr + c, v);
+                tmem_ld_wait();
+                if (c + 16 == BN) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty(buf));  // the last columns are in registers
+                    PROF(1)
+                }
+                if (w.nparts == 1) {
+                    if (p < rowsP) {
 #pragma unroll
-            for (int j = 0; j < BN; ++j) __stcg(mine + j * kRowsP + row, (int32_t)v[j] >> 8);
+                        for (int j = 0; j < 16; ++j)
+                            if (q0 + c + j < rowsQ) C[(int64_t)(q0 + c + j) * ldc + p] = (int32_t)v[j] >> 8;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) __stcg(mine + (c + j) * kRowsP + row, (int32_t)v[j] >> 8);
+                }
+            }
+            if (w.nparts == 1) continue;
             __threadfence();
             __syncwarp();
             int last = 0;
@@ -405,13 +493,12 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
             last = __shfl_sync(0xFFFFFFFFu, last, 0);
             if (!last) continue;
             __threadfence();
-#pragma unroll
+#pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 int32_t sum[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sum[j] = (int32_t)v[c + j] >> 8;  // this partition's share is still in registers
+                for (int j = 0; j < 16; ++j) sum[j] = 0;
                 for (int sk = 0; sk < w.nparts; ++sk) {
-                    if (sk == w.part) continue;
                     const int32_t *src = parts + (int64_t)sk * (kRowsP * BN) + c * kRowsP + row;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) sum[j] += __ldcg(src + j * kRowsP);
@@ -500,13 +587,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     break;
                 }
                 PROF(0)
-                const uint32_t src = pk0 + ps * Cfg::kPkStage + kH * kPkSubP;  // both sub-blocks, contiguous
-                uint4 w[Cfg::kQIters];
-#pragma unroll
-                for (int j = 0; j < Cfg::kQIters; ++j) w[j] = lds128(src + (j * kQConvThreads + ctid) * 16);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pk_empty(ps));
-                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -517,13 +597,24 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 }
                 PROF(2)
                 tc_fence_after_sync();
+                const uint32_t src = pk0 + ps * Cfg::kPkStage + kH * kPkSubP;  // both sub-blocks, contiguous
                 const uint32_t dst = cv0 + cs * Cfg::kCvStage;
+                constexpr int kBatch = Cfg::kQIters < 4 ? Cfg::kQIters : 4;
+#pragma unroll 1
+                for (int j0 = 0; j0 < Cfg::kQIters; j0 += kBatch) {
+                    uint4 wq[kBatch];
 #pragma unroll
-                for (int j = 0; j < Cfg::kQIters; ++j) {
-                    const int i = j * kQConvThreads + ctid;  // chunk index over [sub-block][row][4]
-                    const int sub = i / (BN * 4), rem = i % (BN * 4);
-                    convert_chunk_to_smem(dst + sub * Cfg::kCvSubQ, rem >> 2, rem & 3, w[j]);
+                    for (int j = 0; j < kBatch; ++j) wq[j] = lds128(src + ((j0 + j) * kQConvThreads + ctid) * 16);
+#pragma unroll
+                    for (int j = 0; j < kBatch; ++j) {
+                        const int i = (j0 + j) * kQConvThreads + ctid;  // chunk index over [sub-block][row][4]
+                        const int sub = i / (BN * 4), rem = i % (BN * 4);
+                        convert_chunk_to_smem(dst + sub * Cfg::kCvSubQ, rem >> 2, rem & 3, wq[j]);
+                    }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pk_empty(ps));
+                PROF(1)
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(cv_full(cs));
@@ -536,25 +627,31 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
     // ------------------------------ teardown ------------------------------
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CL) {
+        // peers may still be writing into this CTA's receive slots (always, if this CTA gave up on a wait)
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, kTmemCols);
+        tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
     }
 }
 
-template <int BN>
+template <int BN, int R, bool CL>
 int prepare_one()
 {
-    cudaError_t e = cudaFuncSetAttribute(gemm_dec_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecCfg<BN>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_dec_kernel<BN, R, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         DecCfg<BN, R, CL>::kSmemBytes);
     if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(shared memory)");
     return QM_OK;
 }
 
-template <int BN>
+template <int BN, int R, bool CL>
 int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanced, int32_t *scratch, size_t scratch_bytes,
                int *counters, int num_counters)
 {
-    using Cfg = DecCfg<BN>;
+    using Cfg = DecCfg<BN, R, CL>;
     const int rowsP = g.n, rowsQ = g.m;
     const int64_t kbytes = g.k / 2;
     CUtensorMap tmP, tmQ;
@@ -567,7 +664,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
     const int tilesQ = (rowsQ + BN - 1) / BN;
     const int64_t tiles = (int64_t)tilesP * tilesQ;
     const int num_kb = (g.k + kH * 128 - 1) / (kH * 128);
-    const int sms = ctx.num_sms > 0 ? ctx.num_sms : 1;
+    const int sms = (ctx.num_sms > 0 ? ctx.num_sms : 1) * R;  // CTA slots
     if (tiles > 0x7FFFFFFF / 64) return QM_ERR_SHAPE;
     int units, parts_stride;
     if (balanced) {
@@ -582,8 +679,12 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
         const int64_t items = tiles * split_k;
         units = items < sms ? (int)items : sms;
         parts_stride = split_k;
+        if (CL) {
+            if (split_k < 2 || split_k > 4 || items > 0x7FFFFFFF) return QM_ERR_ARG;
+            units = (int)items;  // one piece per CTA, the pieces of a tile are one cluster
+        }
     }
-    if (parts_stride > 1) {
+    if (parts_stride > 1 && !CL) {
         if ((size_t)tiles * parts_stride * kRowsP * BN * sizeof(int32_t) > scratch_bytes || tiles * 4 > num_counters)
             return QM_ERR_WORKSPACE;
         if (!scratch || !counters) return QM_ERR_NULL;
@@ -593,17 +694,24 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
     cfg.numAttrs = 0;
     static const bool allow_pdl = !std::getenv("QM_NO_PDL");
     if (allow_pdl) {
         // may begin while the previous kernel of the stream drains; the kernel itself waits before global accesses
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.numAttrs = 1;
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_dec_kernel<BN>, tmP, tmQ, g.C, g.ldc, rowsP, rowsQ, g.k, ctx.status, split_k,
+    if (CL) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+        attr[cfg.numAttrs].val.clusterDim.x = (unsigned)split_k;
+        attr[cfg.numAttrs].val.clusterDim.y = 1;
+        attr[cfg.numAttrs].val.clusterDim.z = 1;
+        ++cfg.numAttrs;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_dec_kernel<BN, R, CL>, tmP, tmQ, g.C, g.ldc, rowsP, rowsQ, g.k, ctx.status, split_k,
                                        parts_stride, scratch, counters);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_dec_kernel launch");
     return QM_OK;
@@ -613,20 +721,39 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
 
 int dec_prepare_device()
 {
-    int st = prepare_one<16>();
-    if (st == QM_OK) st = prepare_one<32>();
-    if (st == QM_OK) st = prepare_one<64>();
+    int st = prepare_one<16, 1, false>();
+    if (st == QM_OK) st = prepare_one<32, 1, false>();
+    if (st == QM_OK) st = prepare_one<64, 1, false>();
+    if (st == QM_OK) st = prepare_one<16, 2, false>();
+    if (st == QM_OK) st = prepare_one<16, 1, true>();
+    if (st == QM_OK) st = prepare_one<32, 1, true>();
+    if (st == QM_OK) st = prepare_one<64, 1, true>();
     return st;
 }
 
 int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx)
 {
+    const bool bal = p.stream_k == 1;
+#define QM_DEC_ARGS g, ctx, p.split_k, bal, ctx.scratch, ctx.scratch_bytes, ctx.counters, ctx.num_counters
+    if (p.ctas_per_sm == 2) {
+        if (p.tile_n != 16 || p.stream_k == 2) return QM_ERR_ARG;
+        return launch_one<16, 2, false>(QM_DEC_ARGS);
+    }
+    if (p.stream_k == 2) {  // K partitions of a tile = one cluster, summed through its shared memory
+        switch (p.tile_n) {
+        case 16: return launch_one<16, 1, true>(QM_DEC_ARGS);
+        case 32: return launch_one<32, 1, true>(QM_DEC_ARGS);
+        case 64: return launch_one<64, 1, true>(QM_DEC_ARGS);
+        default: return QM_ERR_ARG;
+        }
+    }
     switch (p.tile_n) {
-    case 16: return launch_one<16>(g, ctx, p.split_k, p.stream_k != 0, ctx.scratch, ctx.scratch_bytes, ctx.counters, ctx.num_counters);
-    case 32: return launch_one<32>(g, ctx, p.split_k, p.stream_k != 0, ctx.scratch, ctx.scratch_bytes, ctx.counters, ctx.num_counters);
-    case 64: return launch_one<64>(g, ctx, p.split_k, p.stream_k != 0, ctx.scratch, ctx.scratch_bytes, ctx.counters, ctx.num_counters);
+    case 16: return launch_one<16, 1, false>(QM_DEC_ARGS);
+    case 32: return launch_one<32, 1, false>(QM_DEC_ARGS);
+    case 64: return launch_one<64, 1, false>(QM_DEC_ARGS);
     default: return QM_ERR_ARG;
     }
+#undef QM_DEC_ARGS
 }
 
 #ifdef QM_DEC_PROFILE

@@ -52,7 +52,9 @@ struct TcPlan {
     int cta_pair;  // 1 or 2
     int a_tmem;    // 1: the UMMA-M operand goes through TMEM: gemm_tc2_kernel (256 x 256 pair tile) or, with swap_ab,
                    //    gemm_dec_kernel (decode form)
-    int stream_k;  // 1 (gemm_dec_kernel only): one equal contiguous share of the (tile, K) work per SM instead of split_k
+    int stream_k;  // gemm_dec_kernel only: 0 = split_k partitions through scratch, 1 = one equal contiguous share of the
+                   // (tile, K) work per CTA, 2 = split_k partitions as one cluster, summed through its shared memory
+    int ctas_per_sm;  // gemm_dec_kernel only: 1 or 2 resident CTAs per SM (2: tile_n 16 only)
 };
 
 // qm_gemm_tc.cu

@@ -37,7 +37,7 @@ inline bool tc_eligible(const GemmArgs &g)
 
 inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
-    TcPlan p{256, 0, 1, 1, 0, 0};
+    TcPlan p{256, 0, 1, 1, 0, 0, 1};
     for (const PlanRule &r : kPlanRules) {
         if (m <= r.m_max) {
             p.tile_n = r.tile_n;
@@ -56,9 +56,24 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
         if (s > num_kb / 2) s = num_kb / 2;
         p.split_k = s < 1 ? 1 : s;
         p.a_tmem = 1;
-        // More tiles than SMs: whole tiles leave the last round partly empty (224 tiles on 148 SMs: 34.7 us),
-        // equal contiguous shares of the (tile, K) work do not (29.6 us; 16 x 57344 x 8192: 52 us = 4.6 TB/s).
-        if (tiles > num_sms) p.stream_k = 1, p.split_k = 1;
+        // Wide token tiles have large partial tiles (128 x 32 or 128 x 64 int32): their K partitions run as one
+        // thread-block cluster and add up through its shared memory (32 x 4096 x 4096: 10.6 -> 9.1 us, 64 x 4096 x 4096:
+        // 13.7 -> 11.4 us, 64 x 8192 x 8192: 18.5 -> 16.7 us).  With 16 tokens the scratch path is as fast (7.9 vs 8.1 us).
+        if (p.tile_n >= 32 && p.split_k >= 2) p.stream_k = 2;
+        if (p.tile_n == 16 && tiles > num_sms / 2) {
+            // Enough tiles to put two smaller CTAs on every SM, which hide each other's pipeline bubbles:
+            // 16 x 11008 x 4096 (86 tiles) 11.6 -> 10.3 us with 3 K partitions, 16 x 28672 x 8192 (224 tiles)
+            // 29.6 -> 26.5 us.  Below that the CTAs of one launch end up paired on half of the SMs (16 x 4096 x 4096:
+            // 9.0 us against 7.9 us with one CTA per SM).
+            p.ctas_per_sm = 2;
+            s = (2 * num_sms + tiles / 2) / tiles;
+            if (s > 4) s = 4;
+            if (s > num_kb / 2) s = num_kb / 2;
+            p.split_k = s < 1 ? 1 : s;
+        }
+        // More tiles than CTA slots: whole tiles leave the last round partly empty, equal contiguous shares of the
+        // (tile, K) work do not (16 x 57344 x 8192, 448 tiles: 48.2 us = 4.9 TB/s).
+        if (tiles > num_sms * p.ctas_per_sm) p.stream_k = 1, p.split_k = 1;
     }
     if (!p.swap_ab) {
         // narrow outputs: do not spend a 256-wide tile on fewer columns

@@ -32,6 +32,12 @@ def variants(m: int, n: int):
                 for sk in (1, 2, 3, 4, 5, 6, 8):
                     out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk, a_tmem=2))
                 out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, a_tmem=2, stream_k=2))
+                for sk in (2, 3, 4):  # the K partitions of a tile as one cluster
+                    out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk, a_tmem=2, stream_k=3))
+                if tn == 16:  # two smaller CTAs per SM
+                    for sk in (1, 2, 3, 4):
+                        out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, split_k=sk, a_tmem=2, ctas_per_sm=2))
+                    out.append(dict(tile_n=tn, swap_ab=2, cta_pair=1, a_tmem=2, stream_k=2, ctas_per_sm=2))
     if m > 64:
         for tn in (128, 256):
             out.append(dict(tile_n=tn, swap_ab=1, cta_pair=1, split_k=1))

@@ -80,7 +80,12 @@ def test_plan(qm):
     assert qm.plan(128, 4096, 4096)["a_tmem"] == 2 and qm.plan(128, 4096, 4096)["split_k"] == 4
     d = qm.plan(16, 4096, 4096)
     assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16 and d["a_tmem"] == 2
-    assert d["stream_k"] == 1 and qm.plan(16, 28672, 8192)["stream_k"] == 2  # more tiles than SMs: equal shares
+    assert d["stream_k"] == 1 and d["ctas_per_sm"] == 1 and d["split_k"] == 4
+    big = qm.plan(16, 57344, 8192)  # more tiles than CTA slots: equal shares, two CTAs per SM
+    assert big["stream_k"] == 2 and big["ctas_per_sm"] == 2
+    assert qm.plan(16, 11008, 4096)["ctas_per_sm"] == 2 and qm.plan(16, 11008, 4096)["split_k"] == 3
+    wide = qm.plan(64, 4096, 4096)  # wide token tile: K partitions as one cluster
+    assert wide["stream_k"] == 3 and wide["split_k"] == 4 and wide["tile_n"] == 64
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -103,9 +108,12 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
                 assert 1 <= p["split_k"] <= max(1, blocks)
                 if swap:
                     assert m <= 64 and p["tile_n"] in (16, 32, 64) and p["tile_n"] >= m and not pair and tm
-                    assert p["stream_k"] == 1 or p["split_k"] == 1
+                    assert p["stream_k"] in (1, 3) or p["split_k"] == 1
+                    if p["stream_k"] == 3:  # cluster form: wide token tiles, 2..4 partitions, one CTA per SM
+                        assert p["tile_n"] >= 32 and 2 <= p["split_k"] <= 4 and p["ctas_per_sm"] == 1
+                    assert p["ctas_per_sm"] == 1 or (p["ctas_per_sm"] == 2 and p["tile_n"] == 16)
                 else:
-                    assert p["stream_k"] == 1
+                    assert p["stream_k"] == 1 and p["ctas_per_sm"] == 1
                 if tm and not swap:
                     assert pair and p["tile_n"] == 256
                 if pair:

@@ -100,25 +100,30 @@ def test_split_k_through_scratch(qm, cuda_clean, oracle, golden, split_k):
 
 
 @pytest.mark.parametrize("tile_n", [16, 32, 64])
-@pytest.mark.parametrize("split_k", [1, 2, 3, 4, 8, "balanced"])
+@pytest.mark.parametrize("split_k", [1, 2, 3, 4, 8, "balanced", "cluster2", "cluster3", "cluster4"])
 def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, tile_n, split_k):
     """gemm_dec_kernel: B rows on UMMA-M, converted in registers and fed to the MMA from TMEM.  Ragged n, m above and
     below the tile, a K tail inside a 256-element stage, several tiles per CTA, and twice in a row (arrival counters).
     "balanced" cuts the (tile, K) work into one equal contiguous share per SM instead of K partitions per tile."""
     if split_k == "balanced":
         opts = dict(tc(tile_n, 2, 1, 0), a_tmem=2, stream_k=2)
+    elif isinstance(split_k, str):  # the K partitions of a tile are one cluster and add up through its shared memory
+        opts = dict(tc(tile_n, 2, 1, int(split_k[-1])), a_tmem=2, stream_k=3)
     else:
         opts = dict(tc(tile_n, 2, 1, split_k), a_tmem=2)
+    variants = [opts] + ([dict(opts, ctas_per_sm=2)] if tile_n == 16 and not str(split_k).startswith("cluster") else [])  # two smaller CTAs per SM
     cases = [(16, 1024, 4096), (1, 384, 2048), (64, 1280, 2048), (40, 200, 4096), (7, 130, 2080), (100, 5000, 2048)]
     for m, n, k in cases:
         ap = oracle.fill_packed(m, k, 61); bp = oracle.fill_packed(n, k, 62)
         want = oracle.gemm(ap, bp)
-        for _ in range(2):
-            _check(qm, cuda_clean, oracle, ap, bp, want=want, **opts)
+        for o in variants:
+            for _ in range(2):
+                _check(qm, cuda_clean, oracle, ap, bp, want=want, **o)
     if split_k in (1, "balanced"):
         for name, g in golden.items():
-            got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **opts)
-            assert np.array_equal(got, g["c"]), f"{name} tile_n={tile_n}: " + mismatch_report(got, g["c"])
+            for o in variants:
+                got = run_gemm(qm, cuda_clean, g["a_packed"], g["b_packed"], **o)
+                assert np.array_equal(got, g["c"]), f"{name} {o}: " + mismatch_report(got, g["c"])
         ap = oracle.fill_packed(3, 32, 63); bp = oracle.fill_packed(129, 32, 64)  # one MMA slice of K
         _check(qm, cuda_clean, oracle, ap, bp, **opts)
 
