@@ -300,10 +300,21 @@ def native_arm(args) -> None:
     if large and args.gather == "nccl" and world > 1:
         full_c = torch.empty((m, n_total), dtype=torch.int32, device="cuda")
 
+    dq = None
+    if args.dequant:
+        # fused dequantising epilogue (qm_gemm_s4_dequant_bf16): bf16 output, per-row and per-column scales
+        if world != 1 or forced or large:
+            raise SystemExit("bench.py: --dequant is a single-GPU option without forced tiles")
+        dq = (torch.rand(m, device="cuda") * 0.01 + 1e-3, torch.rand(n_local, device="cuda") * 0.01 + 1e-3,
+              [torch.empty((m, n_local), dtype=torch.bfloat16, device="cuda") for _ in range(rotate)])
+        per_launch_bytes = m * k // 2 + b_bytes + 2 * m * n_local + 4 * (m + n_local)
+
     def launch():
         i = counter[0] % rotate
         counter[0] += 1
-        if forced:
+        if dq is not None:
+            qm.gemm_dequant(a, bs[i], dq[0], dq[1], dq[2][i], m, n_local, k, workspace=cs[i].view(-1))
+        elif forced:
             qm.gemm_ex(a, bs[i], cs[i], m, n_local, k, kernel=1, **forced)
         elif csym is not None:
             sh.local_into(a, bs[i], m, k, csym, dst=0)  # epilogue stores go to rank 0's C over NVLink
@@ -399,8 +410,10 @@ def native_arm(args) -> None:
                 cfg["l2"] = f"{rotate} distinct B and C buffers in rotation ({rotate * per_launch_bytes / 1e6:.0f} MB) exceed the 126 MB L2"
         if args.graph:
             cfg["cuda_graph_launches_per_step"] = launches_per_step
+        if dq is not None:
+            cfg["epilogue"] = "fused dequantisation to bf16 (row and column scales), not the int32 store of the headline metric"
         line = {
-            "metric": METRIC if not (custom or large) else f"int4 GEMM TOPS at M={m} N={n_total} K={k}",
+            "metric": (METRIC if not (custom or large) else f"int4 GEMM TOPS at M={m} N={n_total} K={k}") + (" (bf16 dequant epilogue)" if dq is not None else ""),
             "value": value,
             "unit": UNIT,
             "n_gpus": world,
@@ -522,6 +535,8 @@ def main() -> None:
                     help="large: M=N=K=32768 with B column-sharded over the GPUs (strong scaling)")
     ap.add_argument("--gather", choices=["none", "nccl", "fused"], default="none",
                     help="with --workload large: also bring the full C to every rank (nccl) or to rank 0 (fused) inside each step")
+    ap.add_argument("--dequant", action="store_true",
+                    help="time qm_gemm_s4_dequant_bf16 (bf16 output with row and column scales) instead of the int32 GEMM")
     ap.add_argument("--op", choices=["gemm", "pack", "unpack"], default="gemm",
                     help="pack / unpack: time the HBM-bound byte kernels on a --shape ROWS,K matrix instead of the GEMM")
     args = ap.parse_args()

@@ -17,6 +17,7 @@
 #ifndef QUADMUL_B200_H
 #define QUADMUL_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -164,6 +165,23 @@ int qm_device_status(int *code, int *where, int clear);
  */
 int qm_gemm_s4_static_scratch(const void *A, const void *B, void *C, int m, int n, int k, int split_k,
                               void *stream);
+
+/*
+ * The GEMM with a fused dequantising epilogue, for W4A4 inference: out[r][c] (bfloat16, row pitch ldc elements) =
+ * bf16( float(sum) * scale_a[r] * scale_b[c] ), where sum is the exact int32 dot product, float() and bf16() round to
+ * nearest even and the two multiplications are separate fp32 operations in that order (the CPU oracle repeats exactly
+ * these steps, so results are compared bit for bit).  scale_a (m floats, per row of A / token) and scale_b (n floats, per
+ * row of B / output channel) are device pointers; NULL means all ones.  It has no counterpart in the reference, whose
+ * only epilogue is the int32 store (reference kernel.cu:155-184; README.md:7 names fusing as the intended use).
+ *   Shapes that run the 256 x 256 large-shape kernel (m > 64, n > 128, k % 32 == 0, A, B and out 16-byte aligned,
+ *   ldc % 8 == 0) convert inside the GEMM epilogue and never write the int32 matrix: C traffic drops from 4 to 2 bytes
+ *   per element and `workspace` is not touched.  Every other shape computes the int32 product into `workspace`
+ *   (m * n * 4 bytes, device memory, 4-byte aligned; QM_ERR_WORKSPACE if smaller) and converts in a second pass.
+ *   qm_gemm_s4_dequant_workspace_bytes tells which: 0 = fused (for 16-byte-aligned A and B).
+ */
+int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, const float *scale_b, void *out_bf16, int m, int n,
+                            int k, int64_t ldc, void *workspace, size_t workspace_bytes, void *stream);
+size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, const void *out_bf16);
 
 /* What the dispatcher would run for (m, n, k): fills *opts with the resolved choices. */
 int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts);

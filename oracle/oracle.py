@@ -186,6 +186,27 @@ def np_gemm(a_packed: np.ndarray, b_packed: np.ndarray) -> np.ndarray:
     return c.astype(np.int32)
 
 
+def bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns (uint16), round to nearest even (finite inputs)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def dequant_bf16(acc: np.ndarray, scale_a: np.ndarray | None, scale_b: np.ndarray | None) -> np.ndarray:
+    """The fused epilogue of qm_gemm_s4_dequant_bf16 restated: bf16(float32(acc) * scale_a[r] * scale_b[c]) as uint16 bit
+    patterns; int32 -> float32 rounds to nearest even, the two products are separate float32 multiplications in this
+    order.  The reference has no such epilogue (its store is kernel.cu:155-184); this defines the contract of the added
+    entry point."""
+    f = acc.astype(np.float32)
+    if scale_a is not None:
+        f = f * np.asarray(scale_a, dtype=np.float32)[:, None]
+    else:
+        f = f * np.float32(1.0)
+    if scale_b is not None:
+        f = f * np.asarray(scale_b, dtype=np.float32)[None, :]
+    return bf16_bits(f)
+
+
 def random_s4(rows: int, K: int, seed: int) -> np.ndarray:
     """Uniform on [-8, 7] (both ends included), int8."""
     return np.random.default_rng(seed).integers(-8, 8, size=(rows, K), dtype=np.int8)

@@ -124,6 +124,43 @@ def gemm_ex(a, b, c, m: int, n: int, k: int, *, kernel: int = 0, tile_n: int = 0
     _launches += 1
 
 
+def gemm_dequant(a, b, scale_a, scale_b, out, m: int, n: int, k: int, workspace=None):
+    """out[m, n] (bfloat16) = bf16(float(A @ B^T) * scale_a[:, None] * scale_b[None, :]) (qm_gemm_s4_dequant_bf16).
+
+    a, b: packed int4 as in `gemm`; scale_a [m] and scale_b [n]: float32 CUDA tensors or None (all ones); out: bfloat16,
+    row-major with unit column stride (a column slab of a wider tensor is fine).  Large shapes convert inside the GEMM
+    epilogue; the others need an int32 workspace of m * n elements, which is allocated here when not passed in."""
+    global _launches
+    torch = _torch()
+    if not (a.is_cuda and b.is_cuda and out.is_cuda) or a.device != b.device or a.device != out.device:
+        raise ValueError("gemm_dequant: a, b, out must be CUDA tensors on one device (there is no CPU path)")
+    if a.dtype not in (torch.int8, torch.uint8) or b.dtype not in (torch.int8, torch.uint8) or out.dtype != torch.bfloat16:
+        raise ValueError("gemm_dequant: a, b must be int8/uint8 (packed), out bfloat16")
+    if not a.is_contiguous() or not b.is_contiguous() or out.dim() != 2 or out.stride(1) != 1:
+        raise ValueError("gemm_dequant: a, b contiguous, out row-major")
+    if a.numel() != m * (k // 2) or b.numel() != n * (k // 2) or tuple(out.shape) != (m, n) or k % 2:
+        raise ValueError("gemm_dequant: shapes do not match (m, n, k)")
+    for name, sc, cnt in (("scale_a", scale_a, m), ("scale_b", scale_b, n)):
+        if sc is not None and (sc.dtype != torch.float32 or not sc.is_cuda or sc.device != a.device or not sc.is_contiguous()
+                               or sc.numel() != cnt):
+            raise ValueError(f"gemm_dequant: {name} must be a contiguous float32 CUDA tensor of {cnt} elements")
+    ldc = out.stride(0) if m > 1 else max(out.stride(0), n)
+    need = LIB.qm_gemm_s4_dequant_workspace_bytes(m, n, k, ldc, out.data_ptr())
+    if (a.data_ptr() | b.data_ptr()) & 15:
+        need = m * n * 4  # unaligned operands never take the fused kernel
+    if need and workspace is None:
+        workspace = torch.empty(need // 4, dtype=torch.int32, device=a.device)
+    ws_ptr = workspace.data_ptr() if workspace is not None else None
+    ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    with _on_device(a):
+        st = LIB.qm_gemm_s4_dequant_bf16(a.data_ptr(), b.data_ptr(), scale_a.data_ptr() if scale_a is not None else None,
+                                         scale_b.data_ptr() if scale_b is not None else None, out.data_ptr(), m, n, k, ldc,
+                                         ws_ptr, ws_bytes, _stream_of(a))
+    check(st, f"quadmul.gemm_dequant(m={m}, n={n}, k={k})")
+    _launches += 1 if not need else 2
+    return out
+
+
 def gemm_host(a, b, c, m: int, n: int, k: int) -> None:
     """Host-buffer form (qm_gemm_s4_host): a, b, c are CPU tensors or numpy arrays; copies in, runs
     on the current device, copies out, synchronises."""

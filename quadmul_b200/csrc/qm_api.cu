@@ -241,6 +241,45 @@ int qm_gemm_s4_ldc_ex(const void *A, const void *B, void *C, int m, int n, int k
     return gemm_dispatch(A, B, C, m, n, k, ldc, stream, opts);
 }
 
+int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, const float *scale_b, void *out_bf16, int m, int n,
+                            int k, int64_t ldc, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int st = check_gemm_args(A, B, out_bf16, m, n, k, ldc);
+    if (st != QM_OK) return st;
+    if (m == 0 || n == 0) return QM_OK;
+    DeviceCtx *ctx = nullptr;
+    st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (k > 0) {
+        GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), nullptr, m, n, k, ldc, s};
+        g.out_bf16 = out_bf16, g.scale_a = scale_a, g.scale_b = scale_b;
+        const TcPlan p = plan_tc(m, n, k, ctx->num_sms);
+        // fused: the large-shape kernel converts inside its epilogue and never writes the int32 matrix
+        if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
+    }
+    // composed: int32 product into the caller's workspace, then one element-wise pass
+    const size_t need = (size_t)m * (size_t)n * sizeof(int32_t);
+    if (!workspace || workspace_bytes < need) return QM_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 3u) != 0) return QM_ERR_ALIGN;
+    st = gemm_dispatch(A, B, workspace, m, n, k, n, stream, nullptr);
+    if (st != QM_OK) return st;
+    return dequant_launch(static_cast<const int32_t *>(workspace), n, scale_a, scale_b, out_bf16, ldc, m, n, s);
+}
+
+size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, const void *out_bf16)
+{
+    if (m <= 0 || n <= 0 || k < 0) return 0;
+    if (k > 0 && k % 32 == 0 && k < 131072) {
+        GemmArgs g{nullptr, nullptr, nullptr, m, n, k, ldc, nullptr};
+        g.out_bf16 = out_bf16 ? const_cast<void *>(out_bf16) : reinterpret_cast<void *>(uintptr_t(16));  // NULL: assume aligned
+        const TcPlan p = plan_tc(m, n, k, 148);
+        // the operands are assumed 16-byte aligned here; an unaligned A or B takes the composed path and needs the workspace
+        if (p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return 0;
+    }
+    return (size_t)m * (size_t)n * sizeof(int32_t);
+}
+
 int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int k)
 {
     int st = check_gemm_args(hA, hB, hC, m, n, k, n);

@@ -6,6 +6,8 @@
 // then reads it back with consecutive lanes on consecutive 16-byte pieces of a row, so each global store
 // instruction writes whole contiguous row segments (128 bytes per row for CH = 32).
 #pragma once
+#include <cuda_bf16.h>
+
 #include "qm_ptx.cuh"
 
 namespace qm {
@@ -116,6 +118,44 @@ __device__ __forceinline__ void store_block_tma(const uint32_t (&v)[32], uint32_
     if (lane == 0) {
         if (accumulate) tma_reduce_add_2d(tmapC, buf, col0, row0);
         else tma_store_2d(tmapC, buf, col0, row0);
+        tma_store_commit();
+    }
+}
+
+// ---- fused dequantisation --------------------------------------------------------------------
+// One output element: the exact int32 sum as float (round to nearest even), times the row scale, times the column
+// scale (two separate fp32 multiplications, in this order), rounded to nearest even bf16.  The CPU oracle does the same
+// four steps, so the results agree bit for bit.
+__device__ __forceinline__ uint32_t dequant_bf16_bits(int32_t sum, float sa, float sb)
+{
+    const float f = __fmul_rn(__fmul_rn(__int2float_rn(sum), sa), sb);
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// va / vb = 256 x two neighbouring 32 x 32 accumulator blocks (columns col0 .. col0 + 31 and col0 + 32 .. col0 + 63), one
+// row per lane; `sa` = this lane's row scale; lane j of sb0 / sb1 holds the scale of column col0 + j / col0 + 32 + j.
+// Writes the 32 x 64 bf16 block (128-byte rows, 128-byte-swizzled like the tensor map) and hands it to the TMA engine.
+__device__ __forceinline__ void store_pair_bf16_tma(const uint32_t (&va)[32], const uint32_t (&vb)[32], uint32_t buf, int lane,
+                                                    const void *tmapOut, int col0, int row0, float sa, float sb0, float sb1)
+{
+    const uint32_t row = buf + lane * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = (c & 3) * 8 + 2 * i;  // column inside the 32-column block
+            const float s0 = __shfl_sync(0xFFFFFFFFu, c < 4 ? sb0 : sb1, j);
+            const float s1 = __shfl_sync(0xFFFFFFFFu, c < 4 ? sb0 : sb1, j + 1);
+            const int32_t x0 = (int32_t)(c < 4 ? va[j] : vb[j]) >> 8, x1 = (int32_t)(c < 4 ? va[j + 1] : vb[j + 1]) >> 8;
+            o[i] = dequant_bf16_bits(x0, sa, s0) | (dequant_bf16_bits(x1, sa, s1) << 16);
+        }
+        ptx::sts128(row + (((uint32_t)c ^ ((uint32_t)lane & 7u)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tmapOut, buf, col0, row0);
         tma_store_commit();
     }
 }

@@ -142,11 +142,13 @@ __device__ __forceinline__ void tmem_st_wait()
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-template <int H, bool MC>
+// DQ = fused dequantising epilogue: tmapC describes a bf16 output, every element is the int32 sum times scale_a[row] times
+// scale_b[column] rounded to bf16 (qm_epilogue.cuh); stores go through TMA only and K is not split.
+template <int H, bool MC, bool DQ>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                 const __grid_constant__ CUtensorMap tmapC, int use_tma_store, int32_t *__restrict__ C, int64_t ldc, int M,
-                int N, int K, int *status, int split_k)
+                int N, int K, int *status, int split_k, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
 {
     using Cfg = Tc2Cfg<H>;
     constexpr int S = Cfg::S, SP = Cfg::SP;
@@ -347,6 +349,37 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 }
             };
             uint32_t va[32], vb[32];
+            if constexpr (DQ) {
+                // this lane's row scale and, spread over the lanes, the scales of the warp's 128 columns
+                const int row = row0 + lane;
+                const float sa = (scale_a && row < M) ? __ldg(scale_a + row) : 1.0f;
+                float sb[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int col = q0 + 32 * i + lane;
+                    sb[i] = (scale_b && col < N) ? __ldg(scale_b + col) : 1.0f;
+                }
+                tmem_ld_x32(taddr, va);
+                tmem_ld_x32(taddr + 32, vb);
+                tmem_ld_wait();
+                if (buf_used) {
+                    if (lane == 0) tma_store_wait_read<0>();
+                    __syncwarp();
+                }
+                store_pair_bf16_tma(va, vb, buf, lane, &tmapC, q0, row0, sa, sb[0], sb[1]);
+                buf_used = true;
+                tmem_ld_x32(taddr + 64, va);
+                tmem_ld_x32(taddr + 96, vb);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
+                PROF(1)
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+                store_pair_bf16_tma(va, vb, buf, lane, &tmapC, q0 + 64, row0, sa, sb[2], sb[3]);
+                continue;
+            }
             tmem_ld_x32(taddr, va);
             tmem_ld_x32(taddr + 32, vb);
             tmem_ld_wait();
@@ -495,10 +528,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     }
 }
 
-template <int H, bool MC>
+template <int H, bool MC, bool DQ>
 int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
-    auto kernel = gemm_tc2_kernel<H, MC>;
+    auto kernel = gemm_tc2_kernel<H, MC, DQ>;
     const int64_t kbytes = g.k / 2;
     CUtensorMap tmA, tmB;
     int st = make_packed_tmap(&tmA, g.A, g.m, kbytes, kRowsA, CU_TENSOR_MAP_SWIZZLE_64B);
@@ -511,10 +544,15 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
     if (tiles > 0x7FFFFFFF / 4) return QM_ERR_SHAPE;
     // TMA store of C needs a 16-byte-aligned base and row pitch; otherwise the kernel stores with plain vectors
     static const bool allow_tma_store = !std::getenv("QM_NO_TMA_STORE");
-    const int use_tma_store =
+    int use_tma_store =
         (allow_tma_store && !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && g.ldc < (1ll << 36)) ? 1 : 0;
     CUtensorMap tmC = tmA;  // placeholder when unused
-    if (use_tma_store) {
+    if (DQ) {
+        if (split_k != 1 || !tc2_can_dequant(g)) return QM_ERR_ALIGN;
+        use_tma_store = 1;
+        st = make_out_bf16_tmap(&tmC, g.out_bf16, g.m, g.n, g.ldc);
+        if (st != QM_OK) return st;
+    } else if (use_tma_store) {
         st = make_c_tmap(&tmC, g.C, g.m, g.n, g.ldc);
         if (st != QM_OK) return st;
     }
@@ -551,7 +589,8 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
     if (units < 1) units = 1;
     if (tiles < units) units = (int)tiles;
     cfg.gridDim = dim3((unsigned)(units * 2), 1, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k, g.scale_a,
+                                       g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc2_kernel launch");
     return QM_OK;
 }
@@ -560,13 +599,13 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 
 // Built variants (sub-blocks per stage, pair-wide commit).  Measured at 8192^3 on B200 before the TMA-store epilogue:
 // (1, false) 442 us, (1, true) 418 us, (2, false) 337 us, (2, true) 328 us; only the fastest is compiled in.
-#define QM_TC2_FOR_EACH(X) X(2, true)
+#define QM_TC2_FOR_EACH(X) X(2, true, false) X(2, true, true)
 
 int tc2_prepare_device()
 {
     cudaError_t e;
-#define X(H, MC)                                                                                                          \
-    e = cudaFuncSetAttribute(gemm_tc2_kernel<H, MC>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Cfg<H>::kSmemBytes); \
+#define X(H, MC, DQ)                                                                                                          \
+    e = cudaFuncSetAttribute(gemm_tc2_kernel<H, MC, DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Cfg<H>::kSmemBytes); \
     if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(shared memory)");
     QM_TC2_FOR_EACH(X)
 #undef X
@@ -580,7 +619,17 @@ bool tc2_can_split(const GemmArgs &g)
 
 int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
 {
-    return tc2_launch_variant<2, true>(g, ctx, split_k);
+    return tc2_launch_variant<2, true, false>(g, ctx, split_k);
+}
+
+bool tc2_can_dequant(const GemmArgs &g)
+{
+    return g.out_bf16 && (reinterpret_cast<uintptr_t>(g.out_bf16) & 15u) == 0 && (g.ldc & 7) == 0 && g.ldc < (1ll << 37);
+}
+
+int tc2_launch_dequant(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    return tc2_launch_variant<2, true, true>(g, ctx, 1);
 }
 
 #ifdef QM_TC2_PROFILE

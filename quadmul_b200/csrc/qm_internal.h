@@ -42,6 +42,11 @@ struct GemmArgs {
     int64_t ldc;
     cudaStream_t stream;
     bool plain_stores = false;  // write C with ordinary vector stores only (destination in another GPU's memory)
+    // fused dequantisation (qm_gemm_s4_dequant_bf16): out[r][c] = bf16(float(sum) * scale_a[r] * scale_b[c]); C is unused,
+    // ldc counts bf16 elements; a NULL scale vector means all ones
+    void *out_bf16 = nullptr;
+    const float *scale_a = nullptr;
+    const float *scale_b = nullptr;
 };
 
 // Resolved tensor-path plan (see qm_tile_table.h for how it is chosen).
@@ -69,6 +74,12 @@ int tc_counters_needed(int m, int n, const TcPlan &p);
 int tc2_prepare_device();
 int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k);
 bool tc2_can_split(const GemmArgs &g);  // K partitions accumulate through TMA reduce-add: needs an aligned local C
+bool tc2_can_dequant(const GemmArgs &g);  // the fused bf16 epilogue stores with TMA only: aligned out, ldc % 8 == 0
+int tc2_launch_dequant(const GemmArgs &g, const DeviceCtx &ctx);
+
+// qm_dequant.cu: out[r][c] = bf16(float(acc[r][c]) * scale_a[r] * scale_b[c]) for an int32 matrix already in memory
+int dequant_launch(const int32_t *acc, int64_t ld_acc, const float *scale_a, const float *scale_b, void *out_bf16, int64_t ldc,
+                   int m, int n, cudaStream_t s);
 
 // qm_gemm_dec.cu: decode form (swap_ab, tile_n 16/32/64), B rows through TMEM; split-K through the context's scratch
 int dec_prepare_device();

@@ -112,5 +112,22 @@ inline int make_c_tmap(CUtensorMap *map, const int32_t *C, int m, int n, int64_t
     return QM_OK;
 }
 
+// The bf16 output of the fused dequantising epilogue as a 2-D tensor [m][n] with row pitch ldc; 64 x 32 boxes (128-byte
+// rows), 128-byte swizzle.
+inline int make_out_bf16_tmap(CUtensorMap *map, const void *out, int m, int n, int64_t ldc)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return record_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point");
+    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)ldc * 2};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(out), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(bf16 out)");
+    return QM_OK;
+}
+
 }  // namespace tc
 }  // namespace qm

@@ -128,6 +128,27 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
         _check(qm, cuda_clean, oracle, ap, bp, **opts)
 
 
+@pytest.mark.parametrize("m,n,k,expect", [
+    (16, 4096, 4096, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),      # K partitions through scratch
+    (32, 4096, 4096, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
+    (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
+    (1, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
+    (64, 11008, 4096, dict(tile_n=64, split_k=1, ctas_per_sm=1)),
+    (16, 28672, 8192, dict(tile_n=16, split_k=1, stream_k=1, ctas_per_sm=2)),     # 224 tiles on 296 CTA slots
+    (5, 38016, 2048, dict(tile_n=16, stream_k=2, ctas_per_sm=2)),                 # 297 tiles: equal shares
+])
+def test_decode_shapes_through_the_table(qm, cuda_clean, oracle, m, n, k, expect):
+    """The decode configurations (and two larger ones) exactly as qm_gemm_s4 runs them, against the full oracle."""
+    plan = qm.plan(m, n, k)
+    assert plan["swap_ab"] == 2 and plan["a_tmem"] == 2
+    for key, val in expect.items():
+        assert plan[key] == val, (key, plan)
+    ap = oracle.fill_packed(m, k, 71); bp = oracle.fill_packed(n, k, 72)
+    want = oracle.gemm(ap, bp)
+    for _ in range(2):
+        _check(qm, cuda_clean, oracle, ap, bp, want=want)
+
+
 # ------------------------------------------------------------------ seeded random shapes
 @pytest.mark.parametrize(
     "m,n,k",

@@ -73,3 +73,21 @@ def test_against_reference_binary_if_present(oracle):
         ap, bp = oracle.pack(a), oracle.pack(b)
         assert np.array_equal(oracle.ref_unpack(ap), a) and np.array_equal(oracle.ref_unpack(bp), b)
         assert np.array_equal(oracle.ref_cpu_gemm(a, b), oracle.gemm(ap, bp))
+
+
+def test_dequant_restatement_rounds_like_torch(oracle):
+    """int32 -> float32 -> two float32 products -> bfloat16 (nearest even): numpy restatement against torch on the CPU."""
+    import torch
+
+    rng = np.random.default_rng(5)
+    acc = rng.integers(-(2**31), 2**31 - 1, size=(37, 53), dtype=np.int64).astype(np.int32)
+    acc[0, :8] = [0, 1, -1, 2**24 + 1, -(2**24) - 1, 2**31 - 1, -(2**31), 12345678]
+    sa = rng.uniform(1e-3, 2.0, size=37).astype(np.float32)
+    sb = rng.uniform(1e-3, 2.0, size=53).astype(np.float32)
+    got = oracle.dequant_bf16(acc, sa, sb)
+    t = (torch.from_numpy(acc).to(torch.float32) * torch.from_numpy(sa)[:, None]) * torch.from_numpy(sb)[None, :]
+    want = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(got, want)
+    ones = oracle.dequant_bf16(acc, None, None)
+    want1 = torch.from_numpy(acc).to(torch.float32).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(ones, want1)
