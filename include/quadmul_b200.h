@@ -174,8 +174,9 @@ int qm_gemm_s4_static_scratch(const void *A, const void *B, void *C, int m, int 
  * row of B / output channel) are device pointers; NULL means all ones.  It has no counterpart in the reference, whose
  * only epilogue is the int32 store (reference kernel.cu:155-184; README.md:7 names fusing as the intended use).
  *   Shapes that run the 256 x 256 large-shape kernel (m > 64, n > 128, k % 32 == 0, A, B and out 16-byte aligned,
- *   ldc % 8 == 0) convert inside the GEMM epilogue and never write the int32 matrix: C traffic drops from 4 to 2 bytes
- *   per element and `workspace` is not touched.  Every other shape computes the int32 product into `workspace`
+ *   ldc % 8 == 0) or the decode kernel (m <= 64, k % 32 == 0, A and B 16-byte aligned) convert inside the GEMM
+ *   epilogue and never write the int32 matrix: C traffic drops from 4 to 2 bytes per element and `workspace` is not
+ *   touched.  Every other shape computes the int32 product into `workspace`
  *   (m * n * 4 bytes, device memory, 4-byte aligned; QM_ERR_WORKSPACE if smaller) and converts in a second pass.
  *   qm_gemm_s4_dequant_workspace_bytes tells which: 0 = fused (for 16-byte-aligned A and B).
  */

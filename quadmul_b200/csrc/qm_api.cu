@@ -255,8 +255,20 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
         GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), nullptr, m, n, k, ldc, s};
         g.out_bf16 = out_bf16, g.scale_a = scale_a, g.scale_b = scale_b;
         const TcPlan p = plan_tc(m, n, k, ctx->num_sms);
-        // fused: the large-shape kernel converts inside its epilogue and never writes the int32 matrix
+        // fused: the large-shape and the decode kernel convert inside their epilogues and never write the int32 matrix
         if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
+        if (tc_eligible(g) && p.a_tmem && p.swap_ab) {
+            TcPlan q = p;
+            if (q.split_k > 1 && q.stream_k != 2 &&
+                (tc_scratch_bytes_needed(m, n, q) > ctx->scratch_bytes || tc_counters_needed(m, n, q) > ctx->num_counters))
+                q.split_k = 1;
+            st = dec_launch(g, q, *ctx);
+            if (st == QM_ERR_WORKSPACE && q.stream_k == 1) {
+                q.stream_k = 0, q.split_k = 1;
+                st = dec_launch(g, q, *ctx);
+            }
+            return st;
+        }
     }
     // composed: int32 product into the caller's workspace, then one element-wise pass
     const size_t need = (size_t)m * (size_t)n * sizeof(int32_t);
@@ -276,6 +288,7 @@ size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, cons
         const TcPlan p = plan_tc(m, n, k, 148);
         // the operands are assumed 16-byte aligned here; an unaligned A or B takes the composed path and needs the workspace
         if (p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return 0;
+        if (p.a_tmem && p.swap_ab) return 0;  // decode kernel: any alignment of out
     }
     return (size_t)m * (size_t)n * sizeof(int32_t);
 }

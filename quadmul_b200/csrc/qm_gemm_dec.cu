@@ -32,7 +32,9 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
+#include "qm_epilogue.cuh"
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
 #include "qm_tc_common.cuh"
@@ -214,8 +216,11 @@ template <int BN, int R, bool CL>
 __global__ void __launch_bounds__(kNumThreads, R)
 gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
                 int32_t *__restrict__ C, int64_t ldc, int rowsP, int rowsQ, int K, int *status, int split_k, int parts_stride,
-                int32_t *__restrict__ scratch, int *__restrict__ counters)
+                int32_t *__restrict__ scratch, int *__restrict__ counters, uint16_t *__restrict__ out_bf16,
+                const float *__restrict__ scale_a, const float *__restrict__ scale_b)
 {
+    // out_bf16 != NULL: fused dequantisation, out[q][p] = bf16(float(sum) * scale_a[q] * scale_b[p]) instead of C[q][p] = sum
+    // (q = row of A, p = row of B; a NULL scale vector is all ones).
     // split_k >= 1: K partitions per tile (parts_stride = split_k); split_k == 0: balanced shares, at most parts_stride
     // pieces per tile.  Piece `part` of tile `tile` owns scratch slot tile * parts_stride + part.
     using Cfg = DecCfg<BN, R, CL>;
@@ -402,6 +407,24 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
             const int row = quarter * 32 + lane;
             const int p = (tile % tilesP) * kRowsP + row;  // row of B = column of C
             const int q0 = (tile / tilesP) * BN;           // first row of A = row of C
+            // CNT finished elements of column p, rows q_first .. q_first + CNT - 1 (values >> SHIFT): int32 store, or the
+            // dequantised bf16 store.  The choice is made once per call, outside the unrolled loops.
+            auto put_cols = [&](auto shift_tag, const auto &vals, int first, int q_first) {
+                constexpr int SHIFT = decltype(shift_tag)::value;
+                if (p >= rowsP) return;
+                if (out_bf16) {
+                    const float sbp = scale_b ? __ldg(scale_b + p) : 1.0f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (q_first + j < rowsQ)
+                            out_bf16[(int64_t)(q_first + j) * ldc + p] = (uint16_t)dequant_bf16_bits(
+                                (int32_t)vals[first + j] >> SHIFT, scale_a ? __ldg(scale_a + q_first + j) : 1.0f, sbp);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (q_first + j < rowsQ) C[(int64_t)(q_first + j) * ldc + p] = (int32_t)vals[first + j] >> SHIFT;
+                }
+            };
             if constexpr (CL) {
                 if (w.nparts > 1) {
                     // One piece per CTA, cluster rank = piece.  Row = lane, BN int32 per row, 16-byte chunks XOR-swizzled
@@ -446,11 +469,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                                 v[4 * c] += x.x, v[4 * c + 1] += x.y, v[4 * c + 2] += x.z, v[4 * c + 3] += x.w;
                             }
                         }
-                        if (p < rowsP) {
 #pragma unroll
-                            for (int j = 0; j < BN; ++j)
-                                if (q0 + j < rowsQ) C[(int64_t)(q0 + j) * ldc + p] = (int32_t)v[j];
-                        }
+                        for (int c = 0; c < BN; c += 16) put_cols(std::integral_constant<int, 0>{}, v, c, q0 + c);
                     }
                     continue;
                 }
@@ -471,11 +491,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     PROF(1)
                 }
                 if (w.nparts == 1) {
-                    if (p < rowsP) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (q0 + c + j < rowsQ) C[(int64_t)(q0 + c + j) * ldc + p] = (int32_t)v[j] >> 8;
-                    }
+                    put_cols(std::integral_constant<int, 8>{}, v, 0, q0 + c);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) __stcg(mine + (c + j) * kRowsP + row, (int32_t)v[j] >> 8);
@@ -503,11 +519,7 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j) sum[j] += __ldcg(src + j * kRowsP);
                 }
-                if (p < rowsP) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (q0 + c + j < rowsQ) C[(int64_t)(q0 + c + j) * ldc + p] = sum[j];
-                }
+                put_cols(std::integral_constant<int, 0>{}, sum, 0, q0 + c);
             }
         }
         PROF(2)
@@ -712,7 +724,7 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
         ++cfg.numAttrs;
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_dec_kernel<BN, R, CL>, tmP, tmQ, g.C, g.ldc, rowsP, rowsQ, g.k, ctx.status, split_k,
-                                       parts_stride, scratch, counters);
+                                       parts_stride, scratch, counters, static_cast<uint16_t *>(g.out_bf16), g.scale_a, g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_dec_kernel launch");
     return QM_OK;
 }

@@ -150,8 +150,21 @@ template <bool kRemote>
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane)
 {
     if constexpr (!kRemote) {
-        const bool ok = mbar_wait(bar, parity, abort_flag);
-        return __all_sync(0xFFFFFFFFu, ok);
+        // Every lane polls (each lane needs its own acquire of the data the barrier guards), but all lanes leave the
+        // loop in the same iteration: one try_wait can answer differently for different lanes of a warp when the phase
+        // completes while the instruction is in flight, and lanes that left a per-lane loop at different times ran
+        // the warp-wide .sync.aligned tcgen05 instructions that follow (tcgen05.st / tcgen05.ld) out of step, which
+        // showed as a few stale TMEM lanes about once in 10^7 waits.
+        if (__all_sync(0xFFFFFFFFu, mbar_try_wait(bar, parity))) return true;
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        for (;;) {
+            if (__all_sync(0xFFFFFFFFu, mbar_try_wait(bar, parity))) return true;
+            if ((++spins & 63u) == 0u) {
+                const bool stop = (*abort_flag != 0) || (globaltimer_ns() - t0 > QM_WAIT_LIMIT_NS);
+                if (__any_sync(0xFFFFFFFFu, stop)) return false;
+            }
+        }
     } else {
         int ok = 1;
         if (lane == 0) ok = mbar_spin_wait(bar, parity, abort_flag) ? 1 : 0;

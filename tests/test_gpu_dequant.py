@@ -39,8 +39,11 @@ def _bits(t):
     (1000, 1000, 2048, True),
     (257, 136, 64, True),        # one row and eight columns into the second tile
     (300, 516, 512, False),      # row pitch not a multiple of 8 elements: int32 product + second pass
-    (16, 1024, 1024, False),     # decode kernel + second pass
-    (64, 4096, 512, False),
+    (16, 1024, 1024, True),      # decode kernel, K partitions through scratch, converts when the last partition sums
+    (64, 4096, 512, True),       # decode kernel, K partitions as one cluster
+    (7, 11008, 1024, True),      # decode kernel, two CTAs per SM, ragged tokens
+    (40, 300, 96, True),         # decode kernel, unsplit
+    (5, 38016, 512, True),       # decode kernel, equal shares
     (200, 100, 512, False),      # narrow output: single-CTA tile + second pass
     (33, 47, 30, False),         # dp4a kernel + second pass
 ])
@@ -97,7 +100,7 @@ def test_dequant_reports_a_missing_workspace(qm, cuda_clean, oracle):
     torch = cuda_clean
     from quadmul_b200._lib import LIB
 
-    m, n, k = 16, 256, 256
+    m, n, k = 200, 100, 256  # narrow output: no fused epilogue, the int32 product needs the workspace
     a, b = to_dev(torch, oracle.fill_packed(m, k, 1)), to_dev(torch, oracle.fill_packed(n, k, 2))
     out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     st = LIB.qm_gemm_s4_dequant_bf16(a.data_ptr(), b.data_ptr(), None, None, out.data_ptr(), m, n, k, n, None, 0, None)

@@ -368,6 +368,15 @@ def test_two_streams_run_large_gemms_concurrently(qm, cuda_clean, oracle):
 
 
 # ------------------------------------------------------------------ full-size configs
+def _where_differs(torch, got, want):
+    """Which 32 x 32 blocks of two equal-shaped matrices differ (for the assertion message)."""
+    bad = (got != want)
+    idx = bad.nonzero()
+    blocks = sorted({(int(r) // 32, int(c) // 32) for r, c in idx[:100000].tolist()})
+    first = [(int(r), int(c), int(got[r, c]), int(want[r, c])) for r, c in idx[:6].tolist()]
+    return f"{int(bad.sum())} elements differ in {len(blocks)} 32x32 blocks {blocks[:24]}; first (row, col, got, want): {first}"
+
+
 def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     torch = cuda_clean
     m = n = k = 8192
@@ -389,7 +398,7 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     assert np.array_equal(got, oracle.gemm_points(ap, bp, rows, cols))
     # (3) the whole matrix against an independent GPU computation: unpack kernel + cuBLASLt int8
     ref = torch._int_mm(qm.unpack(a), qm.unpack(b).t())
-    assert torch.equal(c, ref)
+    assert torch.equal(c, ref), _where_differs(torch, c, ref)
     # (4) linearity in A: with A' = A clamped to [-7, 7], C(-A', B) = -C(A', B)
     ua = qm.unpack(a).clamp_(min=-7)
     c_pos = torch.empty_like(c); c_neg = torch.empty_like(c)
@@ -403,6 +412,35 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     qm.gemm_ex(a, b, c2, m, n, k, kernel=1, tile_n=128, swap_ab=1, cta_pair=1)
     torch.cuda.synchronize()
     assert torch.equal(c, c2)
+
+
+@pytest.mark.parametrize("m,n,k,launches,opts", [
+    (8192, 8192, 8192, 400, {}),                                              # large-shape kernel, 1024 tiles per launch
+    (2048, 4096, 11008, 300, {}),
+    (4096, 4096, 4096, 300, dict(kernel=1, tile_n=128, swap_ab=1, cta_pair=1)),  # single-CTA tile of the general kernel
+    (16, 11008, 4096, 1500, {}),                                              # decode kernel, two CTAs per SM
+    (64, 4096, 4096, 1500, {}),                                               # decode kernel, cluster reduction
+])
+def test_repeated_launches_give_identical_results(qm, cuda_clean, oracle, m, n, k, launches, opts):
+    """The same product many times over: every launch must reproduce the first bit for bit (which is checked against the
+    oracle on row slabs).  Guards the hand-offs between the kernel's warp roles: a hazard there shows as a few wrong
+    rows in a fraction of a per cent of the launches (the per-lane exit from a barrier poll did, 17 times in 2000
+    launches at 8192^3), which a single comparison would miss."""
+    torch = cuda_clean
+    a = qm.fill_packed(m, k, 1002); b = qm.fill_packed(n, k, 2002)
+    first = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    run = (lambda c: qm.gemm_ex(a, b, c, m, n, k, **opts)) if opts else (lambda c: qm.gemm(a, b, c, m, n, k))
+    run(first)
+    torch.cuda.synchronize()
+    ap = a.cpu().numpy().view(np.uint8); bp = b.cpu().numpy().view(np.uint8)
+    rows = min(m, 64)
+    for m0 in sorted({0, (m - rows) // 2, m - rows}):
+        assert np.array_equal(first[m0 : m0 + rows].cpu().numpy(), oracle.gemm(ap, bp, rows=(m0, m0 + rows)))
+    again = torch.empty_like(first)
+    for i in range(launches):
+        again.fill_(-7)
+        run(again)
+        assert torch.equal(again, first), f"launch {i}: " + _where_differs(torch, again, first)
 
 
 def test_large_32768_sampled(qm, cuda_clean, oracle):
