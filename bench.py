@@ -281,7 +281,7 @@ def native_arm(args) -> None:
     # consecutive launches cannot be served from the 126 MB L2
     b_bytes = n_local * (k // 2)
     per_launch_bytes = m * k // 2 + b_bytes + 4 * m * n_local
-    rotate = 1 if per_launch_bytes > 200e6 else min(64, int(2 * 126e6 // max(per_launch_bytes, 1)) + 2)
+    rotate = 1 if (per_launch_bytes > 200e6 or args.l2_resident) else min(64, int(2 * 126e6 // max(per_launch_bytes, 1)) + 2)
     bs = [qm.fill_packed(n_local, k, 2002 + 7919 * rank + 31 * i) for i in range(rotate)]
     cs = [torch.empty((m, n_local), dtype=torch.int32, device="cuda") for _ in range(rotate)]
     c = cs[0]
@@ -385,7 +385,8 @@ def native_arm(args) -> None:
             achieved = per_launch_bytes / (avg_launch_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
         roofline.update({
-            "kernel": (f"gemm_dec_kernel<tile_n={plan['tile_n']}, B rows through TMEM, " +
+            "kernel": ("gemv_kernel<dp4a, weight streaming>" if plan.get("kernel") == 3 and not forced else
+                       f"gemm_dec_kernel<tile_n={plan['tile_n']}, B rows through TMEM, " +
                        ("balanced shares" if plan.get("stream_k") == 2 else f"split_k={plan['split_k']}") + ">"
                        if plan.get("a_tmem") == 2 and plan.get("swap_ab") == 2 else
                        "gemm_tc2_kernel<256x256 pair tile, A in TMEM>" if plan.get("a_tmem") == 2 else
@@ -406,6 +407,8 @@ def native_arm(args) -> None:
         if custom:
             cfg.update({"workload": f"int4 GEMM M={m} N={n_total} K={k} (single GPU, not the headline case)", "m": m,
                         "n_total": n_total, "k": k})
+            if args.l2_resident:
+                cfg["l2"] = "one B and C buffer reused by every launch: served from L2, not an HBM figure"
             if rotate > 1:
                 cfg["l2"] = f"{rotate} distinct B and C buffers in rotation ({rotate * per_launch_bytes / 1e6:.0f} MB) exceed the 126 MB L2"
         if args.graph:
@@ -535,6 +538,9 @@ def main() -> None:
                     help="large: M=N=K=32768 with B column-sharded over the GPUs (strong scaling)")
     ap.add_argument("--gather", choices=["none", "nccl", "fused"], default="none",
                     help="with --workload large: also bring the full C to every rank (nccl) or to rank 0 (fused) inside each step")
+    ap.add_argument("--l2-resident", action="store_true",
+                    help="with --shape: reuse one B and C buffer so that a small problem is served from L2 (the latency floor of "
+                         "the launch; never the roofline number)")
     ap.add_argument("--dequant", action="store_true",
                     help="time qm_gemm_s4_dequant_bf16 (bf16 output with row and column scales) instead of the int32 GEMM")
     ap.add_argument("--op", choices=["gemm", "pack", "unpack"], default="gemm",

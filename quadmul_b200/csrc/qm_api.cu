@@ -109,11 +109,16 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         return e == cudaSuccess ? QM_OK : record_cuda_error(e, "cudaMemset2DAsync");
     }
     int kernel = opts ? opts->kernel : QM_KERNEL_AUTO;
-    if (kernel < QM_KERNEL_AUTO || kernel > QM_KERNEL_SIMT) return QM_ERR_ARG;
+    if (kernel < QM_KERNEL_AUTO || kernel > QM_KERNEL_GEMV) return QM_ERR_ARG;
     const bool eligible = tc_eligible(g);
     if (kernel == QM_KERNEL_TC && !eligible) return QM_ERR_ALIGN;
+    if (kernel == QM_KERNEL_GEMV && !gemv_eligible(g)) return m > kGemvMaxRows ? QM_ERR_ARG : QM_ERR_ALIGN;
+    // one to four rows of A stream the weights through dp4a: faster than the tensor path's pipeline (1 x 4096 x 4096:
+    // see qm_tile_table.h)
+    if (kernel == QM_KERNEL_AUTO && gemv_eligible(g) && gemv_shape_ok(m, n, k)) kernel = QM_KERNEL_GEMV;
     if (kernel == QM_KERNEL_AUTO) kernel = eligible ? QM_KERNEL_TC : QM_KERNEL_SIMT;
     if (kernel == QM_KERNEL_SIMT) return simt_launch(g);
+    if (kernel == QM_KERNEL_GEMV) return gemv_launch(g, *ctx);
 
     TcPlan p = plan_tc(m, n, k, ctx->num_sms);
     if (opts) {
@@ -255,7 +260,8 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
         GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B), nullptr, m, n, k, ldc, s};
         g.out_bf16 = out_bf16, g.scale_a = scale_a, g.scale_b = scale_b;
         const TcPlan p = plan_tc(m, n, k, ctx->num_sms);
-        // fused: the large-shape and the decode kernel convert inside their epilogues and never write the int32 matrix
+        // fused: the large-shape, the decode and the dp4a row kernel convert inside their epilogues and never write the int32 matrix
+        if (gemv_eligible(g) && gemv_shape_ok(m, n, k)) return gemv_launch(g, *ctx);
         if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
         if (tc_eligible(g) && p.a_tmem && p.swap_ab) {
             TcPlan q = p;
@@ -288,7 +294,7 @@ size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, cons
         const TcPlan p = plan_tc(m, n, k, 148);
         // the operands are assumed 16-byte aligned here; an unaligned A or B takes the composed path and needs the workspace
         if (p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return 0;
-        if (p.a_tmem && p.swap_ab) return 0;  // decode kernel: any alignment of out
+        if (p.a_tmem && p.swap_ab) return 0;  // decode kernel (and the dp4a row kernel below it): any alignment of out
     }
     return (size_t)m * (size_t)n * sizeof(int32_t);
 }
@@ -432,7 +438,7 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
         return QM_OK;
     }
     TcPlan p = plan_tc(m, n, k, 148);
-    opts->kernel = QM_KERNEL_TC;
+    opts->kernel = gemv_shape_ok(m, n, k) ? QM_KERNEL_GEMV : QM_KERNEL_TC;
     opts->tile_n = p.tile_n;
     opts->swap_ab = p.swap_ab + 1;
     opts->split_k = p.split_k;

@@ -85,6 +85,21 @@ int dequant_launch(const int32_t *acc, int64_t ld_acc, const float *scale_a, con
 int dec_prepare_device();
 int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
 
+// qm_gemv.cu: one to four rows of A, weight streaming with dp4a (no tensor cores); int32 or fused bf16 output
+constexpr int kGemvMaxRows = 4;
+constexpr size_t kGemvMaxSmemBytes = 200 * 1024;  // converted rows of A held by a CTA
+// Shapes the table gives to the row kernel: one or two rows of A always (HBM-bound at every size: 1 x 28672 x 8192 runs at
+// 4.9 TB/s); three or four rows while the problem is small enough to be latency-bound (4 x 4096 x 4096: 6.3 us against 8.0 us
+// on the tensor path), not beyond (4 x 11008 x 4096: 11.3 against 10.6 us; 4 x 28672 x 8192: 43 against 28 us, dp4a-bound).
+inline bool gemv_shape_ok(int m, int n, int k)
+{
+    if (m < 1 || m > kGemvMaxRows || k % 32 != 0 || k >= 131072) return false;
+    if ((size_t)(m <= 1 ? 1 : (m <= 2 ? 2 : 4)) * (size_t)k > kGemvMaxSmemBytes) return false;
+    return m <= 2 || (int64_t)n * k <= (int64_t)32 * 1024 * 1024;
+}
+bool gemv_eligible(const GemmArgs &g);  // shape limits of the kernel itself (any n) and 16-byte-aligned A and B
+int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx);
+
 // qm_gemm_simt.cu
 int simt_launch(const GemmArgs &g);
 

@@ -21,6 +21,8 @@ DEFAULT_SHAPES = [
 
 def variants(m: int, n: int):
     out = []
+    if m <= 4:
+        out.append(dict(kernel=3))  # dp4a row kernel
     if m <= 256:
         for tn in (16, 32, 64, 128):
             if tn >= min(m, 128) or tn == 128:
@@ -53,12 +55,13 @@ def time_variant(qm, torch, m, n, k, opts, iters, per_graph):
     a = qm.fill_packed(m, k, 1)
     bs = [qm.fill_packed(n, k, 2 + i) for i in range(rotate)]
     cs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(rotate)]
-    qm.gemm_ex(a, bs[0], cs[0], m, n, k, kernel=1, **opts)
+    opts = dict({"kernel": 1}, **opts)
+    qm.gemm_ex(a, bs[0], cs[0], m, n, k, **opts)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         for i in range(per_graph):
-            qm.gemm_ex(a, bs[i % rotate], cs[i % rotate], m, n, k, kernel=1, **opts)
+            qm.gemm_ex(a, bs[i % rotate], cs[i % rotate], m, n, k, **opts)
     g.replay()
     torch.cuda.synchronize()
     best = 1e30

@@ -86,6 +86,8 @@ def test_plan(qm):
     assert qm.plan(16, 11008, 4096)["ctas_per_sm"] == 2 and qm.plan(16, 11008, 4096)["split_k"] == 3
     wide = qm.plan(64, 4096, 4096)  # wide token tile: K partitions as one cluster
     assert wide["stream_k"] == 3 and wide["split_k"] == 4 and wide["tile_n"] == 64
+    assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(4, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(4, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -101,7 +103,8 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
         for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
             for k in (32, 128, 512, 4096, 28672):
                 p = qm.plan(m, n, k)
-                assert p["kernel"] == _lib.QM_KERNEL_TC
+                gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)  # one to four rows: dp4a row kernel
+                assert p["kernel"] == (_lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC)
                 assert p["tile_n"] in (16, 32, 64, 128, 256)
                 swap, pair, tm = p["swap_ab"] == 2, p["cta_pair"] == 2, p["a_tmem"] == 2
                 blocks = (k + 255) // 256 if tm else (k + 127) // 128

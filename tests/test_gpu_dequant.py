@@ -43,6 +43,8 @@ def _bits(t):
     (64, 4096, 512, True),       # decode kernel, K partitions as one cluster
     (7, 11008, 1024, True),      # decode kernel, two CTAs per SM, ragged tokens
     (40, 300, 96, True),         # decode kernel, unsplit
+    (1, 4096, 1024, True),       # dp4a row kernel
+    (3, 1001, 256, True),
     (5, 38016, 512, True),       # decode kernel, equal shares
     (200, 100, 512, False),      # narrow output: single-CTA tile + second pass
     (33, 47, 30, False),         # dp4a kernel + second pass

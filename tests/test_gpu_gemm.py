@@ -132,7 +132,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
     (16, 4096, 4096, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),      # K partitions through scratch
     (32, 4096, 4096, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
     (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
-    (1, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
+    (8, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
     (64, 11008, 4096, dict(tile_n=64, split_k=1, ctas_per_sm=1)),
     (16, 28672, 8192, dict(tile_n=16, split_k=1, stream_k=1, ctas_per_sm=2)),     # 224 tiles on 296 CTA slots
     (5, 38016, 2048, dict(tile_n=16, stream_k=2, ctas_per_sm=2)),                 # 297 tiles: equal shares
@@ -147,6 +147,25 @@ def test_decode_shapes_through_the_table(qm, cuda_clean, oracle, m, n, k, expect
     want = oracle.gemm(ap, bp)
     for _ in range(2):
         _check(qm, cuda_clean, oracle, ap, bp, want=want)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
+    """gemv_kernel (dp4a, weight streaming): what qm_gemm_s4 runs for m <= 4; also forced (kernel=3) and against the tensor
+    path on the same operands.  Odd n (one row of B in the last step), a single K chunk, a long K, twice in a row."""
+    from quadmul_b200 import _lib
+
+    torch = cuda_clean
+    for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (7, 8192), (300, 28672), (2, 64)):
+        assert (qm.plan(m, n, k)["kernel"] == _lib.QM_KERNEL_GEMV) == (m <= 2 or n * k <= 32 * 2**20)
+        ap = oracle.fill_packed(m, k, 91); bp = oracle.fill_packed(n, k, 92)
+        want = oracle.gemm(ap, bp)
+        for opts in ({}, dict(kernel=3), dict(kernel=1)):
+            for _ in range(2):
+                _check(qm, torch, oracle, ap, bp, want=want, **opts)
+    if m == 4:
+        with pytest.raises(qm.QuadmulError):  # five rows are not this kernel's
+            _check(qm, torch, oracle, oracle.fill_packed(5, 64, 1), oracle.fill_packed(8, 64, 2), kernel=3)
 
 
 # ------------------------------------------------------------------ seeded random shapes
@@ -420,6 +439,7 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     (4096, 4096, 4096, 300, dict(kernel=1, tile_n=128, swap_ab=1, cta_pair=1)),  # single-CTA tile of the general kernel
     (16, 11008, 4096, 1500, {}),                                              # decode kernel, two CTAs per SM
     (64, 4096, 4096, 1500, {}),                                               # decode kernel, cluster reduction
+    (1, 11008, 4096, 1500, {}),                                               # dp4a row kernel
 ])
 def test_repeated_launches_give_identical_results(qm, cuda_clean, oracle, m, n, k, launches, opts):
     """The same product many times over: every launch must reproduce the first bit for bit (which is checked against the
@@ -465,3 +485,15 @@ def test_large_32768_sampled(qm, cuda_clean, oracle):
     assert np.array_equal(c[12345].cpu().numpy(), want_row)
     want_col = oracle.gemm(ap, bp[777:778])[:, 0]
     assert np.array_equal(c[:, 777].cpu().numpy(), want_col)
+    # the whole matrix against an independent GPU computation (unpack kernel + cuBLASLt int8), in row slabs
+    if free >= 24 * 2**30:
+        ub = qm.unpack(b).t()
+        for r0 in range(0, m, 4096):
+            ref = torch._int_mm(qm.unpack(a[r0 : r0 + 4096]), ub)
+            assert torch.equal(c[r0 : r0 + 4096], ref), f"rows {r0}..: " + _where_differs(torch, c[r0 : r0 + 4096], ref)
+            del ref
+        # and a second launch must reproduce the first
+        c2 = torch.empty_like(c)
+        qm.gemm(a, b, c2, m, n, k)
+        torch.cuda.synchronize()
+        assert torch.equal(c, c2)
