@@ -27,9 +27,11 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kRowsPerStep = 2;  // rows of B a warp streams at a time
-
-template <int MR>
+// RU = rows of B a warp streams at a time.  Every chunk of a row of A is read from shared memory once per step, so the
+// shared-memory traffic is 2 MR / RU times the weight bytes.  RU = 2 gives twice the warps for a given n (best for the
+// small, latency-bound problems: 2 x 4096 x 4096 4.8 us against 5.8 us), RU = 4 halves the shared-memory traffic (best
+// when the stream is long: 4 x 28672 x 8192 35 against 43 us); the launcher picks by n.
+template <int MR, int RU>
 __global__ void __launch_bounds__(kThreads)
 gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
             uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
@@ -51,6 +53,7 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
     }
     __syncthreads();
 
+    constexpr int kRowsPerStep = RU;
     const int lane = threadIdx.x & 31;
     const int warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
     const int num_warps = gridDim.x * kWarps;
@@ -60,14 +63,15 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
         for (int u = 0; u < kRowsPerStep; ++u)
 #pragma unroll
             for (int r = 0; r < MR; ++r) acc[u][r] = 0;
-        const uint4 *b0 = reinterpret_cast<const uint4 *>(B + (int64_t)row0 * row_bytes);
-        const bool two = row0 + 1 < n;
-        const uint4 *b1 = two ? reinterpret_cast<const uint4 *>(B + (int64_t)(row0 + 1) * row_bytes) : b0;
-#pragma unroll 4
+        const uint4 *brow[kRowsPerStep];  // rows past the end re-read the step's first row; their results are not stored
+#pragma unroll
+        for (int u = 0; u < kRowsPerStep; ++u)
+            brow[u] = reinterpret_cast<const uint4 *>(B + (int64_t)(row0 + u < n ? row0 + u : row0) * row_bytes);
+#pragma unroll(8 / kRowsPerStep)
         for (int c = lane; c < chunks; c += 32) {
             uint4 w[kRowsPerStep];
-            w[0] = __ldcs(b0 + c);
-            w[1] = __ldcs(b1 + c);
+#pragma unroll
+            for (int u = 0; u < kRowsPerStep; ++u) w[u] = __ldcs(brow[u] + c);
             uint4 wl[kRowsPerStep], wh[kRowsPerStep];
 #pragma unroll
             for (int u = 0; u < kRowsPerStep; ++u) tc::split_s4x32(w[u], wl[u], wh[u]);
@@ -120,18 +124,19 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
     }
 }
 
-template <int MR>
+template <int MR, int RU>
 int launch_gemv(const GemmArgs &g, const DeviceCtx &ctx)
 {
     const size_t smem = (size_t)MR * (size_t)g.k;  // MR rows x k int8
     static bool configured[64] = {false};
     if (!configured[ctx.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvMaxSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvMaxSmemBytes);
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(gemv shared memory)");
         configured[ctx.device & 63] = true;
     }
     cudaLaunchConfig_t cfg = {};
     // enough warps that every SM has ~16 rows of B in flight; never more warps than row pairs
+    constexpr int kRowsPerStep = RU;
     const int64_t steps = ((int64_t)g.n + kRowsPerStep - 1) / kRowsPerStep;
     int64_t ctas = (steps + kWarps - 1) / kWarps;
     const int64_t max_ctas = (int64_t)(ctx.num_sms > 0 ? ctx.num_sms : 1) * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
@@ -150,7 +155,7 @@ int launch_gemv(const GemmArgs &g, const DeviceCtx &ctx)
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<MR>, g.A, g.B, g.C, g.ldc, g.m, g.n, g.k, static_cast<uint16_t *>(g.out_bf16),
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<MR, RU>, g.A, g.B, g.C, g.ldc, g.m, g.n, g.k, static_cast<uint16_t *>(g.out_bf16),
                                        g.scale_a, g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemv_kernel launch");
     return QM_OK;
@@ -167,9 +172,10 @@ bool gemv_eligible(const GemmArgs &g)
 int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx)
 {
     if (!gemv_eligible(g)) return QM_ERR_ARG;
-    if (g.m <= 1) return launch_gemv<1>(g, ctx);
-    if (g.m <= 2) return launch_gemv<2>(g, ctx);
-    return launch_gemv<4>(g, ctx);
+    const bool long_stream = g.n >= 16384;
+    if (g.m <= 1) return launch_gemv<1, 2>(g, ctx);
+    if (g.m <= 2) return long_stream ? launch_gemv<2, 4>(g, ctx) : launch_gemv<2, 2>(g, ctx);
+    return long_stream ? launch_gemv<4, 4>(g, ctx) : launch_gemv<4, 2>(g, ctx);
 }
 
 }  // namespace qm
