@@ -386,6 +386,7 @@ def native_arm(args) -> None:
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
         roofline.update({
             "kernel": ("gemv_kernel<dp4a, weight streaming>" if plan.get("kernel") == 3 and not forced else
+                       "gemm_rmma_kernel<weights into registers, mma.sync s8>" if plan.get("kernel") == 4 and not forced else
                        f"gemm_dec_kernel<tile_n={plan['tile_n']}, B rows through TMEM, " +
                        ("balanced shares" if plan.get("stream_k") == 2 else f"split_k={plan['split_k']}") + ">"
                        if plan.get("a_tmem") == 2 and plan.get("swap_ab") == 2 else

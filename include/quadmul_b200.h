@@ -41,7 +41,8 @@ typedef enum qm_kernel {
     QM_KERNEL_AUTO = 0,
     QM_KERNEL_TC = 1,  /* TMA + mbarrier ring + in-smem s4->s8 + tcgen05.mma kind::i8 + TMEM   */
     QM_KERNEL_SIMT = 2, /* dp4a kernel for shapes/alignments the tensor path does not take      */
-    QM_KERNEL_GEMV = 3  /* m <= 4: weight-streaming dp4a kernel (same shape limits as QM_KERNEL_TC) */
+    QM_KERNEL_GEMV = 3, /* m <= 4: weight-streaming dp4a kernel (same shape limits as QM_KERNEL_TC) */
+    QM_KERNEL_RMMA = 4  /* m <= 16, k <= 8192: weights straight into registers, warp-level mma.sync s8     */
 } qm_kernel_t;
 
 /* Options for qm_gemm_s4_ex.  Zero-initialise for defaults. */

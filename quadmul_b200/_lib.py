@@ -59,7 +59,7 @@ SIGNATURES = {
 WRAPPER_MANGLED = "_Z7wrapperPvS_S_iiiP11CUstream_st"
 
 QM_OK = 0
-QM_KERNEL_AUTO, QM_KERNEL_TC, QM_KERNEL_SIMT, QM_KERNEL_GEMV = 0, 1, 2, 3
+QM_KERNEL_AUTO, QM_KERNEL_TC, QM_KERNEL_SIMT, QM_KERNEL_GEMV, QM_KERNEL_RMMA = 0, 1, 2, 3, 4
 
 
 class QuadmulError(RuntimeError):

@@ -1,0 +1,220 @@
+// Packed-int4 GEMM for up to 16 rows of A on small weight matrices: register-resident decode kernel.
+//
+// Same contract as the other GEMM kernels (exact int32 C = A * B^T on nibbles; replaces the reference's igemm<Config>,
+// kernel.cu:62-266).  At the decode sizes named for this library (16 x 4096 x 4096, 16 x 11008 x 4096: 8-23 MB of weights,
+// 1.3-3.5 us of HBM time) a launch of the TMA/TMEM kernel is a chain of hand-offs that costs the same 8-11 us whether
+// the weights come from HBM or from L2.  This kernel has no pipeline to fill: a CTA owns 32 rows of B, its 16 warps split
+// K between them, and every lane asks for ALL of its weights (up to eight 16-byte loads) before anything else happens, so
+// the whole 64 KB block of a CTA is in flight after a few instructions and the launch is one memory round trip long.
+// While the loads fly the CTA converts the rows of A into shared memory (even elements x 16, odd elements x 16 per
+// 16-byte chunk, as everywhere in this library).  The products run on the warp-level tensor path,
+// mma.sync.m16n8k32.s8 (2048 MAC per clock and SM measured on B200, a quarter of tcgen05 but four times what 16 tokens
+// at HBM rate need): A fragment = 16 tokens x 32 K from shared memory, B fragment = 8 rows of B x 32 K straight from
+// the registers the weights were loaded into, after the same x16 split.  Lane (g, q) of a warp (g = lane / 4, q = lane % 4)
+// loads chunk 4 t + q of row g of each of four 8-row groups, and for mma step s = 0..3 supplies word s of the even half as
+// the fragment's k = 4q..4q+3 and word s of the odd half as k = 16+4q..16+4q+3; the A fragment is built from the same
+// words of the same chunks, so every product pairs equal K indices.  The 16 partial 16 x 32 tiles of a CTA meet in shared
+// memory, are summed by 512 threads (one output each), shifted by 8 and stored as 128-byte row segments.
+//
+// Launches chain through programmatic dependent launch; before griddepcontrol.wait a CTA only prefetches its weights into
+// L2 (no data is returned, so this is correct whatever the previous kernel writes).
+#include <cstdlib>
+
+#include "qm_epilogue.cuh"
+#include "qm_internal.h"
+#include "qm_ptx.cuh"
+#include "qm_tc_common.cuh"
+
+namespace qm {
+
+namespace {
+
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRowGroups = 4;               // 8-row groups of B per CTA pass
+constexpr int kRowsPerCta = 8 * kRowGroups;  // 32
+constexpr int kMaxSteps = 2;                // chunk steps a warp keeps in flight at once (8 loads of 16 bytes per lane)
+constexpr int kRedBytes = kWarps * kRowGroups * 32 * 4 * 4;  // 32 KB: one 16 x 32 int32 partial tile per warp
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t word(const uint4 &v, int s) { return s == 0 ? v.x : (s == 1 ? v.y : (s == 2 ? v.z : v.w)); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
+                 uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
+{
+    extern __shared__ uint4 smem_u4[];
+    uint4 *a_cv = smem_u4;  // [16 rows][chunks][2]: even x 16, odd x 16
+    const int chunks = k / 32;
+    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * chunks * 2);  // [warp][row group][lane][4]
+    const int64_t row_bytes = k / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int steps = (chunks + 3) / 4;  // chunk steps of a row: step t covers chunks 4t .. 4t+3
+    const int num_blocks = (n + kRowsPerCta - 1) / kRowsPerCta;
+
+    ptx::grid_launch_dependents();
+    {
+        // L2 prefetch of this CTA's first block of weights: returns no data, touches nothing the program can observe
+        const int rb = blockIdx.x;
+        if (rb < num_blocks) {
+            for (int t = warp; t < steps; t += kWarps) {
+                const int c = 4 * t + q;
+#pragma unroll
+                for (int rg = 0; rg < kRowGroups; ++rg) {
+                    const int row = rb * kRowsPerCta + rg * 8 + g;
+                    if (row < n && c < chunks)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
+                }
+            }
+        }
+    }
+    ptx::grid_dependency_wait();  // nothing above read or wrote global memory
+
+    bool a_ready = false;
+    for (int rb = blockIdx.x; rb < num_blocks; rb += gridDim.x) {
+        int d[kRowGroups][4];
+#pragma unroll
+        for (int rg = 0; rg < kRowGroups; ++rg)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) d[rg][j] = 0;
+
+        for (int t0 = warp; t0 < steps; t0 += kWarps * kMaxSteps) {
+            // all loads of up to kMaxSteps chunk steps first
+            uint4 w[kMaxSteps][kRowGroups];
+#pragma unroll
+            for (int u = 0; u < kMaxSteps; ++u) {
+                const int t = t0 + u * kWarps;
+                const int c = 4 * t + q;
+#pragma unroll
+                for (int rg = 0; rg < kRowGroups; ++rg) {
+                    const int row = rb * kRowsPerCta + rg * 8 + g;
+                    w[u][rg] = make_uint4(0, 0, 0, 0);
+                    if (t < steps && c < chunks && row < n)
+                        w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                }
+            }
+            if (!a_ready) {
+                // the rows of A, once per CTA, while the weights are on their way
+                for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
+                    const int r = i / chunks, c = i - r * chunks;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
+                    uint4 lo, hi;
+                    tc::split_s4x32(v, lo, hi);
+                    a_cv[2 * i] = lo;
+                    a_cv[2 * i + 1] = hi;
+                }
+                __syncthreads();
+                a_ready = true;
+            }
+#pragma unroll
+            for (int u = 0; u < kMaxSteps; ++u) {
+                const int t = t0 + u * kWarps;
+                const int c = 4 * t + q;
+                if (t < steps) {  // uniform over the warp
+                    uint4 alo0 = make_uint4(0, 0, 0, 0), ahi0 = alo0, alo1 = alo0, ahi1 = alo0;
+                    if (c < chunks) {
+                        alo0 = a_cv[2 * (g * chunks + c)], ahi0 = a_cv[2 * (g * chunks + c) + 1];
+                        alo1 = a_cv[2 * ((g + 8) * chunks + c)], ahi1 = a_cv[2 * ((g + 8) * chunks + c) + 1];
+                    }
+#pragma unroll
+                    for (int rg = 0; rg < kRowGroups; ++rg) {
+                        uint4 wl, wh;
+                        tc::split_s4x32(w[u][rg], wl, wh);
+#pragma unroll
+                        for (int s = 0; s < 4; ++s)
+                            mma_s8(d[rg], word(alo0, s), word(alo1, s), word(ahi0, s), word(ahi1, s), word(wl, s), word(wh, s));
+                    }
+                }
+            }
+        }
+        if (!a_ready) {  // a warp count above the step count leaves some warps without loads; the barrier is still shared
+            for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
+                const int r = i / chunks, c = i - r * chunks;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
+                uint4 lo, hi;
+                tc::split_s4x32(v, lo, hi);
+                a_cv[2 * i] = lo;
+                a_cv[2 * i + 1] = hi;
+            }
+            __syncthreads();
+            a_ready = true;
+        }
+        // partial tiles -> shared memory -> one output per thread
+#pragma unroll
+        for (int rg = 0; rg < kRowGroups; ++rg)
+            *reinterpret_cast<int4 *>(red + ((warp * kRowGroups + rg) * 32 + lane) * 4) = make_int4(d[rg][0], d[rg][1], d[rg][2], d[rg][3]);
+        __syncthreads();
+        {
+            const int token = threadIdx.x >> 5, col = threadIdx.x & 31;  // 16 tokens x 32 rows of B
+            const int rg = col >> 3, cc = col & 7;
+            // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
+            const int src_lane = (token & 7) * 4 + (cc >> 1);
+            const int j = (cc & 1) + (token >= 8 ? 2 : 0);
+            int sum = 0;
+#pragma unroll
+            for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 32 + src_lane) * 4 + j];
+            sum >>= 8;
+            const int p = rb * kRowsPerCta + col;
+            if (token < m && p < n) {
+                if (out_bf16)
+                    out_bf16[(int64_t)token * ldc + p] =
+                        (uint16_t)dequant_bf16_bits(sum, scale_a ? __ldg(scale_a + token) : 1.0f, scale_b ? __ldg(scale_b + p) : 1.0f);
+                else
+                    C[(int64_t)token * ldc + p] = sum;
+            }
+        }
+        __syncthreads();  // `red` is rewritten by the next block
+    }
+}
+
+}  // namespace
+
+bool rmma_eligible(const GemmArgs &g)
+{
+    return g.m >= 1 && g.m <= 16 && g.k % 32 == 0 && g.k <= kRmmaMaxK && (reinterpret_cast<uintptr_t>(g.A) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(g.B) & 15u) == 0;
+}
+
+int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    if (!rmma_eligible(g)) return QM_ERR_ARG;
+    const size_t smem = (size_t)16 * g.k + kRedBytes;
+    static bool configured[64] = {false};
+    if (!configured[ctx.device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_rmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * kRmmaMaxK + kRedBytes);
+        if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
+        configured[ctx.device & 63] = true;
+    }
+    const int blocks = (g.n + kRowsPerCta - 1) / kRowsPerCta;
+    const int sms = ctx.num_sms > 0 ? ctx.num_sms : 1;
+    const int per_sm = smem <= 100 * 1024 ? 2 : 1;  // register file: 512 threads x up to 64 registers fit twice
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(blocks < sms * per_sm ? blocks : sms * per_sm), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    static const bool allow_pdl = !std::getenv("QM_NO_PDL");
+    if (allow_pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_rmma_kernel, g.A, g.B, g.C, g.ldc, g.m, g.n, g.k, static_cast<uint16_t *>(g.out_bf16),
+                                       g.scale_a, g.scale_b);
+    if (e != cudaSuccess) return record_cuda_error(e, "gemm_rmma_kernel launch");
+    return QM_OK;
+}
+
+}  // namespace qm

@@ -23,6 +23,8 @@ def variants(m: int, n: int):
     out = []
     if m <= 4:
         out.append(dict(kernel=3))  # dp4a row kernel
+    if m <= 16:
+        out.append(dict(kernel=4))  # register-resident mma.sync kernel (k <= 8192)
     if m <= 256:
         for tn in (16, 32, 64, 128):
             if tn >= min(m, 128) or tn == 128:

@@ -129,7 +129,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
 
 
 @pytest.mark.parametrize("m,n,k,expect", [
-    (16, 4096, 4096, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),      # K partitions through scratch
+    (16, 6144, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=1)),      # K partitions through scratch
     (32, 4096, 4096, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
     (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
     (8, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
@@ -140,7 +140,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
 def test_decode_shapes_through_the_table(qm, cuda_clean, oracle, m, n, k, expect):
     """The decode configurations (and two larger ones) exactly as qm_gemm_s4 runs them, against the full oracle."""
     plan = qm.plan(m, n, k)
-    assert plan["swap_ab"] == 2 and plan["a_tmem"] == 2
+    assert plan["kernel"] == 1 and plan["swap_ab"] == 2 and plan["a_tmem"] == 2
     for key, val in expect.items():
         assert plan[key] == val, (key, plan)
     ap = oracle.fill_packed(m, k, 71); bp = oracle.fill_packed(n, k, 72)
@@ -157,7 +157,8 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
 
     torch = cuda_clean
     for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (7, 8192), (300, 28672), (2, 64), (16503, 256)):  # the last: four rows of B per step
-        assert (qm.plan(m, n, k)["kernel"] == _lib.QM_KERNEL_GEMV) == (m <= 2 or n * k <= 32 * 2**20)
+        if m <= 2:
+            assert qm.plan(m, n, k)["kernel"] == _lib.QM_KERNEL_GEMV
         ap = oracle.fill_packed(m, k, 91); bp = oracle.fill_packed(n, k, 92)
         want = oracle.gemm(ap, bp)
         for opts in ({}, dict(kernel=3), dict(kernel=1)):
@@ -166,6 +167,23 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
     if m == 4:
         with pytest.raises(qm.QuadmulError):  # five rows are not this kernel's
             _check(qm, torch, oracle, oracle.fill_packed(5, 64, 1), oracle.fill_packed(8, 64, 2), kernel=3)
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+def test_register_resident_mma_kernel(qm, cuda_clean, oracle, m):
+    """gemm_rmma_kernel (weights straight into registers, mma.sync s8): forced with kernel=4.  Row counts that are not a
+    multiple of 32, K below one step per warp, K that is not a multiple of 128, the K limit, several blocks per CTA."""
+    torch = cuda_clean
+    for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (37, 96), (64, 8192), (300, 1056), (20000, 256)):
+        ap = oracle.fill_packed(m, k, 93); bp = oracle.fill_packed(n, k, 94)
+        want = oracle.gemm(ap, bp)
+        for _ in range(2):
+            _check(qm, torch, oracle, ap, bp, want=want, kernel=4)
+    if m == 16:
+        with pytest.raises(qm.QuadmulError):
+            _check(qm, torch, oracle, oracle.fill_packed(17, 64, 1), oracle.fill_packed(8, 64, 2), kernel=4)
+        with pytest.raises(qm.QuadmulError):
+            _check(qm, torch, oracle, oracle.fill_packed(4, 8192 + 32, 1), oracle.fill_packed(8, 8192 + 32, 2), kernel=4)
 
 
 # ------------------------------------------------------------------ seeded random shapes
@@ -440,6 +458,8 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     (16, 11008, 4096, 1500, {}),                                              # decode kernel, two CTAs per SM
     (64, 4096, 4096, 1500, {}),                                               # decode kernel, cluster reduction
     (1, 11008, 4096, 1500, {}),                                               # dp4a row kernel
+    (16, 4096, 4096, 1500, {}),                                               # register-resident mma.sync kernel
+    (16, 6144, 4096, 1500, {}),                                               # decode kernel, K partitions through scratch
 ])
 def test_repeated_launches_give_identical_results(qm, cuda_clean, oracle, m, n, k, launches, opts):
     """The same product many times over: every launch must reproduce the first bit for bit (which is checked against the
