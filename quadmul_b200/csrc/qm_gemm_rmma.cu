@@ -50,31 +50,33 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                  uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
 {
     extern __shared__ uint4 smem_u4[];
-    uint4 *a_cv = smem_u4;  // [16 rows][chunks][2]: even x 16, odd x 16
+    uint4 *a_cv = smem_u4;  // [16 rows][chunks][2]: even x 16, odd x 16; rows 16 bytes longer than their data so that the two
+                            // rows a quarter-warp reads at once fall on different banks
     const int chunks = k / 32;
-    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * chunks * 2);  // [warp][row group][lane][4]
+    const int a_stride = 2 * chunks + 1;  // in 16-byte units
+    // [warp][row group][j][32]: accumulator register j of lane l at position (l + 4 (2 rg + (j & 1))) % 32, which makes both the
+    // writes (one register of all lanes) and the reads (one token, 32 rows of B) hit 32 different banks
+    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * a_stride);
     const int64_t row_bytes = k / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int steps = (chunks + 3) / 4;  // chunk steps of a row: step t covers chunks 4t .. 4t+3
     const int num_blocks = (n + kRowsPerCta - 1) / kRowsPerCta;
 
-    ptx::grid_launch_dependents();
-    {
-        // L2 prefetch of this CTA's first block of weights: returns no data, touches nothing the program can observe
-        const int rb = blockIdx.x;
-        if (rb < num_blocks) {
-            for (int t = warp; t < steps; t += kWarps) {
-                const int c = 4 * t + q;
+    // L2 prefetch of one block of weights (this lane's share): returns no data, touches nothing the program can observe
+    auto prefetch_block = [&](int rb) {
+        if (rb >= num_blocks) return;
+        for (int t = warp; t < steps; t += kWarps) {
+            const int c = 4 * t + q;
 #pragma unroll
-                for (int rg = 0; rg < kRowGroups; ++rg) {
-                    const int row = rb * kRowsPerCta + rg * 8 + g;
-                    if (row < n && c < chunks)
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
-                }
+            for (int rg = 0; rg < kRowGroups; ++rg) {
+                const int row = rb * kRowsPerCta + rg * 8 + g;
+                if (row < n && c < chunks) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
             }
         }
-    }
+    };
+    ptx::grid_launch_dependents();
+    prefetch_block((int)blockIdx.x);
     ptx::grid_dependency_wait();  // nothing above read or wrote global memory
 
     bool a_ready = false;
@@ -100,6 +102,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                         w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
                 }
             }
+            // the block this CTA takes next goes to L2 while this one is worked on, so that its loads come back sooner
+            if (t0 == warp) prefetch_block(rb + (int)gridDim.x);
             if (!a_ready) {
                 // the rows of A, once per CTA, while the weights are on their way
                 for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
@@ -108,8 +112,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                     if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
                     uint4 lo, hi;
                     tc::split_s4x32(v, lo, hi);
-                    a_cv[2 * i] = lo;
-                    a_cv[2 * i + 1] = hi;
+                    a_cv[r * a_stride + 2 * c] = lo;
+                    a_cv[r * a_stride + 2 * c + 1] = hi;
                 }
                 __syncthreads();
                 a_ready = true;
@@ -121,8 +125,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 if (t < steps) {  // uniform over the warp
                     uint4 alo0 = make_uint4(0, 0, 0, 0), ahi0 = alo0, alo1 = alo0, ahi1 = alo0;
                     if (c < chunks) {
-                        alo0 = a_cv[2 * (g * chunks + c)], ahi0 = a_cv[2 * (g * chunks + c) + 1];
-                        alo1 = a_cv[2 * ((g + 8) * chunks + c)], ahi1 = a_cv[2 * ((g + 8) * chunks + c) + 1];
+                        alo0 = a_cv[g * a_stride + 2 * c], ahi0 = a_cv[g * a_stride + 2 * c + 1];
+                        alo1 = a_cv[(g + 8) * a_stride + 2 * c], ahi1 = a_cv[(g + 8) * a_stride + 2 * c + 1];
                     }
 #pragma unroll
                     for (int rg = 0; rg < kRowGroups; ++rg) {
@@ -142,8 +146,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
                 uint4 lo, hi;
                 tc::split_s4x32(v, lo, hi);
-                a_cv[2 * i] = lo;
-                a_cv[2 * i + 1] = hi;
+                a_cv[r * a_stride + 2 * c] = lo;
+                a_cv[r * a_stride + 2 * c + 1] = hi;
             }
             __syncthreads();
             a_ready = true;
@@ -151,7 +155,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         // partial tiles -> shared memory -> one output per thread
 #pragma unroll
         for (int rg = 0; rg < kRowGroups; ++rg)
-            *reinterpret_cast<int4 *>(red + ((warp * kRowGroups + rg) * 32 + lane) * 4) = make_int4(d[rg][0], d[rg][1], d[rg][2], d[rg][3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[((warp * kRowGroups + rg) * 4 + j) * 32 + ((lane + 4 * (2 * rg + (j & 1))) & 31)] = d[rg][j];
         __syncthreads();
         {
             const int token = threadIdx.x >> 5, col = threadIdx.x & 31;  // 16 tokens x 32 rows of B
@@ -161,7 +166,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             const int j = (cc & 1) + (token >= 8 ? 2 : 0);
             int sum = 0;
 #pragma unroll
-            for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 32 + src_lane) * 4 + j];
+            for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 4 + j) * 32 + ((src_lane + 4 * (2 * rg + (j & 1))) & 31)];
             sum >>= 8;
             const int p = rb * kRowsPerCta + col;
             if (token < m && p < n) {
@@ -187,10 +192,10 @@ bool rmma_eligible(const GemmArgs &g)
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
 {
     if (!rmma_eligible(g)) return QM_ERR_ARG;
-    const size_t smem = (size_t)16 * g.k + kRedBytes;
+    const size_t smem = (size_t)16 * (g.k + 16) + kRedBytes;  // rows of A are padded by 16 bytes
     static bool configured[64] = {false};
     if (!configured[ctx.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_rmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * kRmmaMaxK + kRedBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_rmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (kRmmaMaxK + 16) + kRedBytes);
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
         configured[ctx.device & 63] = true;
     }

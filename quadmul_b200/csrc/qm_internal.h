@@ -102,12 +102,12 @@ int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx);
 
 // qm_gemm_rmma.cu: up to 16 rows of A on small weight matrices; weights straight into registers, mma.sync s8
 constexpr int kRmmaMaxK = 8192;  // 16 converted rows of A (16 * K bytes) + 32 KB of partial tiles fit in shared memory
-// Shapes the table gives it: 3 to 16 rows of A (one or two go to the row kernel) and a B whose 32-row blocks fit the SMs in
-// one round (16 x 4096 x 4096: 5.2 us against 8.2 us on the TMA/TMEM decode kernel); with several rounds per SM the rounds do not
-// overlap and the decode kernel is faster (16 x 11008 x 4096: 13.0 against 10.5 us).
+// Shapes the table gives it: 3 to 16 rows of A (one or two go to the row kernel) and a B whose 32-row blocks fit the SMs in at
+// most two rounds (16 x 4096 x 4096: 4.7 us against 8.2 us on the TMA/TMEM decode kernel; 16 x 8192 x 4096: 9.4 against 9.8 us).
+// Rounds of one CTA do not overlap, so beyond that the decode kernel is faster (16 x 11008 x 4096: 11.4 against 10.5 us).
 inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
 {
-    return m >= 3 && m <= 16 && k % 32 == 0 && k <= kRmmaMaxK && (n + 31) / 32 <= num_sms;
+    return m >= 3 && m <= 16 && k % 32 == 0 && k <= kRmmaMaxK && (n + 31) / 32 <= 2 * num_sms;
 }
 bool rmma_eligible(const GemmArgs &g);  // limits of the kernel itself (m <= 16, k <= kRmmaMaxK, any n) and 16-byte-aligned A and B
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx);

@@ -78,18 +78,18 @@ def test_plan(qm):
     p = qm.plan(8192, 8192, 8192)
     assert p["kernel"] == _lib.QM_KERNEL_TC and p["tile_n"] == 256 and p["swap_ab"] == 1 and p["cta_pair"] == 2 and p["a_tmem"] == 2
     assert qm.plan(128, 4096, 4096)["a_tmem"] == 2 and qm.plan(128, 4096, 4096)["split_k"] == 4
-    d = qm.plan(16, 6144, 4096)  # decode shape beyond one round of the register-resident kernel
+    d = qm.plan(16, 4096, 16384)  # decode shape beyond the K limit of the register-resident kernel
     assert d["kernel"] == _lib.QM_KERNEL_TC and d["swap_ab"] == 2 and d["tile_n"] >= 16 and d["a_tmem"] == 2
-    assert d["stream_k"] == 1 and d["ctas_per_sm"] == 1 and d["split_k"] == 3
+    assert d["stream_k"] == 1 and d["ctas_per_sm"] == 1 and d["split_k"] == 4
     big = qm.plan(16, 57344, 8192)  # more tiles than CTA slots: equal shares, two CTAs per SM
     assert big["stream_k"] == 2 and big["ctas_per_sm"] == 2
     assert qm.plan(16, 11008, 4096)["ctas_per_sm"] == 2 and qm.plan(16, 11008, 4096)["split_k"] == 3
     wide = qm.plan(64, 4096, 4096)  # wide token tile: K partitions as one cluster
     assert wide["stream_k"] == 3 and wide["split_k"] == 4 and wide["tile_n"] == 64
-    assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 8192, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(4, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(4, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(16, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(16, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
-    assert qm.plan(4, 6144, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(17, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(4, 6144, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(17, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -105,7 +105,7 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
         for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
             for k in (32, 128, 512, 4096, 28672):
                 p = qm.plan(m, n, k)
-                rmma = 3 <= m <= 16 and k <= 8192 and (n + 31) // 32 <= 148  # one round of 32-row blocks: register-resident kernel
+                rmma = 3 <= m <= 16 and k <= 8192 and (n + 31) // 32 <= 296  # at most two rounds of 32-row blocks: register-resident kernel
                 gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)              # one to four rows: dp4a row kernel
                 want = _lib.QM_KERNEL_GEMV if m <= 2 else _lib.QM_KERNEL_RMMA if rmma else _lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC
                 assert p["kernel"] == want

@@ -40,7 +40,7 @@ def _bits(t):
     (257, 136, 64, True),        # one row and eight columns into the second tile
     (300, 516, 512, False),      # row pitch not a multiple of 8 elements: int32 product + second pass
     (16, 1024, 1024, True),      # register-resident mma.sync kernel
-    (16, 6144, 1024, True),      # decode kernel, K partitions through scratch, converts when the last partition sums
+    (16, 2048, 8448, True),      # decode kernel, K partitions through scratch, converts when the last partition sums
     (64, 4096, 512, True),       # decode kernel, K partitions as one cluster
     (7, 11008, 1024, True),      # decode kernel, two CTAs per SM, ragged tokens
     (40, 300, 96, True),         # decode kernel, unsplit

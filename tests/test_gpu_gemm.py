@@ -129,7 +129,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
 
 
 @pytest.mark.parametrize("m,n,k,expect", [
-    (16, 6144, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=1)),      # K partitions through scratch
+    (16, 4096, 16384, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),     # K partitions through scratch (K above the register kernel's limit)
     (32, 4096, 4096, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
     (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
     (8, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
@@ -459,7 +459,7 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     (64, 4096, 4096, 1500, {}),                                               # decode kernel, cluster reduction
     (1, 11008, 4096, 1500, {}),                                               # dp4a row kernel
     (16, 4096, 4096, 1500, {}),                                               # register-resident mma.sync kernel
-    (16, 6144, 4096, 1500, {}),                                               # decode kernel, K partitions through scratch
+    (16, 4096, 16384, 800, {}),                                               # decode kernel, K partitions through scratch
 ])
 def test_repeated_launches_give_identical_results(qm, cuda_clean, oracle, m, n, k, launches, opts):
     """The same product many times over: every launch must reproduce the first bit for bit (which is checked against the
