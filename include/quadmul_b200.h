@@ -151,6 +151,14 @@ int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t sl
 int qm_device_status(int *code, int *where, int clear);
 
 /*
+ * Exercises the time-out path of the kernels without a GEMM: launches one warp that waits, with the same bounded wait the
+ * GEMM kernels use, on a barrier that nothing ever completes.  The wait gives up after its limit (0.2 s), the kernel
+ * returns normally, and qm_device_status then reports QM_ERR_TIMEOUT with wait site 9.  Nothing faults or hangs; the
+ * context stays usable.  No counterpart in the reference (its kernel has no waits that could fail).
+ */
+int qm_selftest_wait_timeout(void *stream);
+
+/*
  * The split-K tensor-core GEMM for callers that must not allocate device memory (a plug-in under a
  * host framework's memory pool or a fixed device-memory budget, a real-time loop that cannot absorb
  * an allocation's stall).  It has no counterpart in the reference.  Same product and layouts as qm_gemm_s4

@@ -235,6 +235,13 @@ def plan(m: int, n: int, k: int) -> dict:
             "a_tmem": o.a_tmem, "stream_k": o.stream_k, "ctas_per_sm": o.ctas_per_sm}
 
 
+def selftest_wait_timeout() -> None:
+    """Launch the one-warp kernel whose bounded wait must expire (qm_selftest_wait_timeout); afterwards device_status()
+    reports (QM_ERR_TIMEOUT, wait site 9).  Takes the wait limit (0.2 s) of GPU time."""
+    torch = _torch()
+    check(LIB.qm_selftest_wait_timeout(torch.cuda.current_stream().cuda_stream), "selftest_wait_timeout")
+
+
 def device_status(clear: bool = True) -> tuple[int, int]:
     """(code, where) of the current device's in-kernel wait status; synchronises the device."""
     code, where = ctypes.c_int(0), ctypes.c_int(0)

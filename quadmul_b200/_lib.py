@@ -50,6 +50,7 @@ SIGNATURES = {
     "qm_unshard_c": (_i, [_vp, _vp, _i, _i, _i, _i64, _vp]),
     "qm_device_status": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), _i]),
     "qm_plan": (_i, [_i, _i, _i, ctypes.POINTER(GemmOpts)]),
+    "qm_selftest_wait_timeout": (_i, [_vp]),
     "qm_gemm_s4_dequant_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp, ctypes.c_size_t, _vp]),
     "qm_gemm_s4_dequant_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i, _i64, _vp]),
     "qm_gemm_s4_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -7,6 +7,7 @@
 #include <string>
 
 #include "qm_internal.h"
+#include "qm_tc_common.cuh"
 #include "qm_tile_table.h"
 
 namespace qm {
@@ -194,6 +195,24 @@ void nshard_range(int n, int world, int rank, int *begin, int *count)
 
 using namespace qm;
 
+// The time-out path of the GEMM kernels in isolation: one warp waits, with the same bounded whole-warp wait the kernels use,
+// on an mbarrier that nothing ever completes; the wait gives up after its limit and records QM_ERR_TIMEOUT / kWaitSelfTest.
+static __global__ void wait_timeout_kernel(int *status)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const bool ok = ptx::warp_wait<false>(ptx::smem_u32(&bar), 0u, &abort_flag, (int)threadIdx.x);
+        if (!ok && threadIdx.x == 0) tc::report_timeout(status, kWaitSelfTest);
+    }
+}
+
 extern "C" {
 
 const char *qm_status_string(int status)
@@ -302,6 +321,16 @@ size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, cons
         if (p.a_tmem && p.swap_ab) return 0;  // decode kernel (and the dp4a row kernel below it): any alignment of out
     }
     return (size_t)m * (size_t)n * sizeof(int32_t);
+}
+
+int qm_selftest_wait_timeout(void *stream)
+{
+    DeviceCtx *ctx = nullptr;
+    int st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    wait_timeout_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(ctx->status);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? QM_OK : record_cuda_error(e, "wait_timeout_kernel launch");
 }
 
 int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int k)

@@ -18,7 +18,8 @@ enum WaitSite : int {
     kWaitMmaOperands = 5,    // MMA issuer waiting for converted operands
     kWaitEpilogueAcc = 6,    // epilogue waiting for a finished accumulator
     kWaitSplitK = 7,         // split-K reducer waiting for partial tiles
-    kWaitPeer = 8            // waiting for the peer CTA of a pair
+    kWaitPeer = 8,           // waiting for the peer CTA of a pair
+    kWaitSelfTest = 9        // qm_selftest_wait_timeout: a barrier that nothing completes
 };
 
 // Per-device state created by qm_init.

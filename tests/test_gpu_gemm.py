@@ -483,6 +483,26 @@ def test_repeated_launches_give_identical_results(qm, cuda_clean, oracle, m, n, 
         assert torch.equal(again, first), f"launch {i}: " + _where_differs(torch, again, first)
 
 
+def test_bounded_wait_expires_and_is_reported(qm, oracle):
+    """A wait that nothing satisfies gives up after its limit, the kernel returns, the status word names the wait, and the
+    next GEMM runs normally (no fault, no hang: the barrier is simply never completed)."""
+    import time
+
+    import torch
+
+    qm.device_status(clear=True)
+    t0 = time.time()
+    qm.selftest_wait_timeout()
+    code, where = qm.device_status(clear=True)  # synchronises
+    elapsed = time.time() - t0
+    assert code == 5 and (where & 0xFF) == 9, (code, where)  # QM_ERR_TIMEOUT at the self-test's wait site
+    assert 0.15 < elapsed < 5.0, elapsed
+    assert qm.device_status(clear=True) == (0, 0)
+    ap = oracle.fill_packed(16, 256, 1); bp = oracle.fill_packed(300, 256, 2)
+    assert np.array_equal(run_gemm(qm, torch, ap, bp), oracle.gemm(ap, bp))
+    assert qm.device_status(clear=True) == (0, 0)
+
+
 def test_large_32768_sampled(qm, cuda_clean, oracle):
     torch = cuda_clean
     m = n = k = 32768
