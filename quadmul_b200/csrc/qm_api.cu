@@ -111,7 +111,7 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
     }
     int kernel = opts ? opts->kernel : QM_KERNEL_AUTO;
     if (kernel < QM_KERNEL_AUTO || kernel > QM_KERNEL_RMMA) return QM_ERR_ARG;
-    if (kernel == QM_KERNEL_RMMA) return rmma_eligible(g) ? rmma_launch(g, *ctx) : ((m > 16 || k > kRmmaMaxK) ? QM_ERR_ARG : QM_ERR_ALIGN);
+    if (kernel == QM_KERNEL_RMMA) return rmma_eligible(g) ? rmma_launch(g, *ctx) : ((m > kRmmaMaxRows || k > (m <= 16 ? kRmmaMaxK : kRmmaMaxKTiled)) ? QM_ERR_ARG : QM_ERR_ALIGN);
     const bool eligible = tc_eligible(g);
     if (kernel == QM_KERNEL_TC && !eligible) return QM_ERR_ALIGN;
     if (kernel == QM_KERNEL_GEMV && !gemv_eligible(g)) return m > kGemvMaxRows ? QM_ERR_ARG : QM_ERR_ALIGN;

@@ -79,105 +79,122 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     prefetch_block((int)blockIdx.x);
     ptx::grid_dependency_wait();  // nothing above read or wrote global memory
 
-    bool a_ready = false;
-    for (int rb = blockIdx.x; rb < num_blocks; rb += gridDim.x) {
-        int d[kRowGroups][4];
+    // rows 16 tt .. 16 tt + 15 of A -> shared memory (zero beyond m); all threads, followed by a barrier
+    auto convert_a = [&](int tt) {
+        for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
+            const int r = i / chunks, c = i - r * chunks;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (16 * tt + r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + (int64_t)(16 * tt + r) * row_bytes) + c);
+            uint4 lo, hi;
+            tc::split_s4x32(v, lo, hi);
+            a_cv[r * a_stride + 2 * c] = lo;
+            a_cv[r * a_stride + 2 * c + 1] = hi;
+        }
+        __syncthreads();
+    };
+    // all loads of up to kMaxSteps chunk steps of block rb, starting at step t0
+    auto load_round = [&](uint4(&w)[kMaxSteps][kRowGroups], int rb, int t0) {
 #pragma unroll
-        for (int rg = 0; rg < kRowGroups; ++rg)
+        for (int u = 0; u < kMaxSteps; ++u) {
+            const int t = t0 + u * kWarps;
+            const int c = 4 * t + q;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) d[rg][j] = 0;
-
-        for (int t0 = warp; t0 < steps; t0 += kWarps * kMaxSteps) {
-            // all loads of up to kMaxSteps chunk steps first
-            uint4 w[kMaxSteps][kRowGroups];
+            for (int rg = 0; rg < kRowGroups; ++rg) {
+                const int row = rb * kRowsPerCta + rg * 8 + g;
+                w[u][rg] = make_uint4(0, 0, 0, 0);
+                if (t < steps && c < chunks && row < n) w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+            }
+        }
+    };
+    // d += (16 rows of A in shared memory) x (the weights of one round)
+    auto mma_round = [&](int(&d)[kRowGroups][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0) {
 #pragma unroll
-            for (int u = 0; u < kMaxSteps; ++u) {
-                const int t = t0 + u * kWarps;
-                const int c = 4 * t + q;
+        for (int u = 0; u < kMaxSteps; ++u) {
+            const int t = t0 + u * kWarps;
+            const int c = 4 * t + q;
+            if (t < steps) {  // uniform over the warp
+                uint4 alo0 = make_uint4(0, 0, 0, 0), ahi0 = alo0, alo1 = alo0, ahi1 = alo0;
+                if (c < chunks) {
+                    alo0 = a_cv[g * a_stride + 2 * c], ahi0 = a_cv[g * a_stride + 2 * c + 1];
+                    alo1 = a_cv[(g + 8) * a_stride + 2 * c], ahi1 = a_cv[(g + 8) * a_stride + 2 * c + 1];
+                }
 #pragma unroll
                 for (int rg = 0; rg < kRowGroups; ++rg) {
-                    const int row = rb * kRowsPerCta + rg * 8 + g;
-                    w[u][rg] = make_uint4(0, 0, 0, 0);
-                    if (t < steps && c < chunks && row < n)
-                        w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
-                }
-            }
-            // the block this CTA takes next goes to L2 while this one is worked on, so that its loads come back sooner
-            if (t0 == warp) prefetch_block(rb + (int)gridDim.x);
-            if (!a_ready) {
-                // the rows of A, once per CTA, while the weights are on their way
-                for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
-                    const int r = i / chunks, c = i - r * chunks;
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
-                    uint4 lo, hi;
-                    tc::split_s4x32(v, lo, hi);
-                    a_cv[r * a_stride + 2 * c] = lo;
-                    a_cv[r * a_stride + 2 * c + 1] = hi;
-                }
-                __syncthreads();
-                a_ready = true;
-            }
+                    uint4 wl, wh;
+                    tc::split_s4x32(w[u][rg], wl, wh);
 #pragma unroll
-            for (int u = 0; u < kMaxSteps; ++u) {
-                const int t = t0 + u * kWarps;
-                const int c = 4 * t + q;
-                if (t < steps) {  // uniform over the warp
-                    uint4 alo0 = make_uint4(0, 0, 0, 0), ahi0 = alo0, alo1 = alo0, ahi1 = alo0;
-                    if (c < chunks) {
-                        alo0 = a_cv[g * a_stride + 2 * c], ahi0 = a_cv[g * a_stride + 2 * c + 1];
-                        alo1 = a_cv[(g + 8) * a_stride + 2 * c], ahi1 = a_cv[(g + 8) * a_stride + 2 * c + 1];
-                    }
-#pragma unroll
-                    for (int rg = 0; rg < kRowGroups; ++rg) {
-                        uint4 wl, wh;
-                        tc::split_s4x32(w[u][rg], wl, wh);
-#pragma unroll
-                        for (int s = 0; s < 4; ++s)
-                            mma_s8(d[rg], word(alo0, s), word(alo1, s), word(ahi0, s), word(ahi1, s), word(wl, s), word(wh, s));
-                    }
+                    for (int s = 0; s < 4; ++s)
+                        mma_s8(d[rg], word(alo0, s), word(alo1, s), word(ahi0, s), word(ahi1, s), word(wl, s), word(wh, s));
                 }
             }
         }
-        if (!a_ready) {  // a warp count above the step count leaves some warps without loads; the barrier is still shared
-            for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
-                const int r = i / chunks, c = i - r * chunks;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + r * row_bytes) + c);
-                uint4 lo, hi;
-                tc::split_s4x32(v, lo, hi);
-                a_cv[r * a_stride + 2 * c] = lo;
-                a_cv[r * a_stride + 2 * c + 1] = hi;
-            }
-            __syncthreads();
-            a_ready = true;
-        }
-        // partial tiles -> shared memory -> one output per thread
+    };
+    // partial tiles of all warps -> shared memory -> one output per thread (token tile tt, block rb); two barriers
+    auto reduce_store = [&](const int(&d)[kRowGroups][4], int rb, int tt) {
 #pragma unroll
         for (int rg = 0; rg < kRowGroups; ++rg)
 #pragma unroll
             for (int j = 0; j < 4; ++j) red[((warp * kRowGroups + rg) * 4 + j) * 32 + ((lane + 4 * (2 * rg + (j & 1))) & 31)] = d[rg][j];
         __syncthreads();
-        {
-            const int token = threadIdx.x >> 5, col = threadIdx.x & 31;  // 16 tokens x 32 rows of B
-            const int rg = col >> 3, cc = col & 7;
-            // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
-            const int src_lane = (token & 7) * 4 + (cc >> 1);
-            const int j = (cc & 1) + (token >= 8 ? 2 : 0);
-            int sum = 0;
+        const int tok = threadIdx.x >> 5, col = threadIdx.x & 31;  // 16 tokens x 32 rows of B
+        const int rg = col >> 3, cc = col & 7;
+        // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
+        const int src_lane = (tok & 7) * 4 + (cc >> 1);
+        const int j = (cc & 1) + (tok >= 8 ? 2 : 0);
+        int sum = 0;
 #pragma unroll
-            for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 4 + j) * 32 + ((src_lane + 4 * (2 * rg + (j & 1))) & 31)];
-            sum >>= 8;
-            const int p = rb * kRowsPerCta + col;
-            if (token < m && p < n) {
-                if (out_bf16)
-                    out_bf16[(int64_t)token * ldc + p] =
-                        (uint16_t)dequant_bf16_bits(sum, scale_a ? __ldg(scale_a + token) : 1.0f, scale_b ? __ldg(scale_b + p) : 1.0f);
-                else
-                    C[(int64_t)token * ldc + p] = sum;
-            }
+        for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 4 + j) * 32 + ((src_lane + 4 * (2 * rg + (j & 1))) & 31)];
+        sum >>= 8;
+        const int token = 16 * tt + tok;
+        const int p = rb * kRowsPerCta + col;
+        if (token < m && p < n) {
+            if (out_bf16)
+                out_bf16[(int64_t)token * ldc + p] =
+                    (uint16_t)dequant_bf16_bits(sum, scale_a ? __ldg(scale_a + token) : 1.0f, scale_b ? __ldg(scale_b + p) : 1.0f);
+            else
+                C[(int64_t)token * ldc + p] = sum;
         }
-        __syncthreads();  // `red` is rewritten by the next block
+        __syncthreads();  // `red` and the rows of A are rewritten next
+    };
+
+    const int tiles = (m + 15) / 16;                       // token tiles of 16 rows of A
+    const bool resident = steps <= kWarps * kMaxSteps;     // a block's weights fit one round of registers (the host requires it for tiles > 1)
+    bool a_ready = false;
+    for (int rb = blockIdx.x; rb < num_blocks; rb += gridDim.x) {
+        int d[kRowGroups][4];
+        uint4 w[kMaxSteps][kRowGroups];
+        if (resident) {
+            // the weights stay in registers while the token tiles pass through shared memory one after the other
+            load_round(w, rb, warp);
+            prefetch_block(rb + (int)gridDim.x);  // the next block goes to L2 meanwhile
+            for (int tt = 0; tt < tiles; ++tt) {
+                if (tiles > 1 || !a_ready) {
+                    convert_a(tt);
+                    a_ready = true;
+                }
+#pragma unroll
+                for (int rg = 0; rg < kRowGroups; ++rg)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) d[rg][j] = 0;
+                mma_round(d, w, warp);
+                reduce_store(d, rb, tt);
+            }
+        } else {
+#pragma unroll
+            for (int rg = 0; rg < kRowGroups; ++rg)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) d[rg][j] = 0;
+            for (int t0 = warp; t0 < steps; t0 += kWarps * kMaxSteps) {
+                load_round(w, rb, t0);
+                if (t0 == warp) prefetch_block(rb + (int)gridDim.x);
+                if (!a_ready) {  // every warp has at least one round here (steps > kWarps * kMaxSteps)
+                    convert_a(0);
+                    a_ready = true;
+                }
+                mma_round(d, w, t0);
+            }
+            reduce_store(d, rb, 0);
+        }
     }
 }
 
@@ -185,7 +202,9 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
 
 bool rmma_eligible(const GemmArgs &g)
 {
-    return g.m >= 1 && g.m <= 16 && g.k % 32 == 0 && g.k <= kRmmaMaxK && (reinterpret_cast<uintptr_t>(g.A) & 15u) == 0 &&
+    // more than one 16-row tile of A needs a block's weights resident in registers: at most kWarps * kMaxSteps chunk steps
+    const int max_k = g.m <= 16 ? kRmmaMaxK : kRmmaMaxKTiled;
+    return g.m >= 1 && g.m <= kRmmaMaxRows && g.k % 32 == 0 && g.k <= max_k && (reinterpret_cast<uintptr_t>(g.A) & 15u) == 0 &&
            (reinterpret_cast<uintptr_t>(g.B) & 15u) == 0;
 }
 

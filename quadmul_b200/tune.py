@@ -23,7 +23,7 @@ def variants(m: int, n: int):
     out = []
     if m <= 4:
         out.append(dict(kernel=3))  # dp4a row kernel
-    if m <= 16:
+    if m <= 64:
         out.append(dict(kernel=4))  # register-resident mma.sync kernel (k <= 8192)
     if m <= 256:
         for tn in (16, 32, 64, 128):
@@ -98,7 +98,7 @@ def main():
             try:
                 ms, code = time_variant(qm, torch, m, n, k, opts, args.iters, per_graph)
             except qm.QuadmulError as exc:
-                if exc.status in (7, 8):  # variant not built, or scratch too small for this split
+                if exc.status in (3, 7, 8):  # variant not built or not for this shape, or scratch too small for this split
                     continue
                 raise
             if code != 0:

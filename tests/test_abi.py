@@ -89,7 +89,7 @@ def test_plan(qm):
     assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(4, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(4, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(16, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(16, 11008, 4096)["kernel"] == _lib.QM_KERNEL_TC
-    assert qm.plan(4, 6144, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(17, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(4, 6144, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(32, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(33, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -105,7 +105,8 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
         for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
             for k in (32, 128, 512, 4096, 28672):
                 p = qm.plan(m, n, k)
-                rmma = 3 <= m <= 16 and k <= 8192 and (n + 31) // 32 <= 296  # at most two rounds of 32-row blocks: register-resident kernel
+                blocks = (n + 31) // 32  # register-resident kernel: 32-row blocks of B, at most two rounds (one with two tiles of A)
+                rmma = (3 <= m <= 16 and k <= 8192 and blocks <= 296) or (17 <= m <= 32 and k <= 4096 and blocks <= 148)
                 gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)              # one to four rows: dp4a row kernel
                 want = _lib.QM_KERNEL_GEMV if m <= 2 else _lib.QM_KERNEL_RMMA if rmma else _lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC
                 assert p["kernel"] == want

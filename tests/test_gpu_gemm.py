@@ -130,7 +130,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
 
 @pytest.mark.parametrize("m,n,k,expect", [
     (16, 4096, 16384, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),     # K partitions through scratch (K above the register kernel's limit)
-    (32, 4096, 4096, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
+    (32, 4096, 8192, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
     (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
     (8, 11008, 4096, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM
     (64, 11008, 4096, dict(tile_n=64, split_k=1, ctas_per_sm=1)),
@@ -169,21 +169,25 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
             _check(qm, torch, oracle, oracle.fill_packed(5, 64, 1), oracle.fill_packed(8, 64, 2), kernel=3)
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 17, 32, 40, 64])
 def test_register_resident_mma_kernel(qm, cuda_clean, oracle, m):
     """gemm_rmma_kernel (weights straight into registers, mma.sync s8): forced with kernel=4.  Row counts that are not a
     multiple of 32, K below one step per warp, K that is not a multiple of 128, the K limit, several blocks per CTA."""
     torch = cuda_clean
     for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (37, 96), (64, 8192), (300, 1056), (20000, 256)):
+        if m > 16 and k > 4096:  # several 16-row tiles of A need the weights of a block resident in registers
+            continue
         ap = oracle.fill_packed(m, k, 93); bp = oracle.fill_packed(n, k, 94)
         want = oracle.gemm(ap, bp)
         for _ in range(2):
             _check(qm, torch, oracle, ap, bp, want=want, kernel=4)
     if m == 16:
         with pytest.raises(qm.QuadmulError):
-            _check(qm, torch, oracle, oracle.fill_packed(17, 64, 1), oracle.fill_packed(8, 64, 2), kernel=4)
+            _check(qm, torch, oracle, oracle.fill_packed(65, 64, 1), oracle.fill_packed(8, 64, 2), kernel=4)
         with pytest.raises(qm.QuadmulError):
             _check(qm, torch, oracle, oracle.fill_packed(4, 8192 + 32, 1), oracle.fill_packed(8, 8192 + 32, 2), kernel=4)
+        with pytest.raises(qm.QuadmulError):
+            _check(qm, torch, oracle, oracle.fill_packed(17, 4096 + 32, 1), oracle.fill_packed(8, 4096 + 32, 2), kernel=4)
 
 
 # ------------------------------------------------------------------ seeded random shapes
