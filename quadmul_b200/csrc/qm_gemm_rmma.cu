@@ -29,12 +29,22 @@ namespace qm {
 
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
-constexpr int kRowGroups = 4;               // 8-row groups of B per CTA pass
-constexpr int kRowsPerCta = 8 * kRowGroups;  // 32
-constexpr int kMaxSteps = 2;                // chunk steps a warp keeps in flight at once (8 loads of 16 bytes per lane)
-constexpr int kRedBytes = kWarps * kRowGroups * 32 * 4 * 4;  // 32 KB: one 16 x 32 int32 partial tile per warp
+// Shape of the CTA: WARPS warps, RG 8-row groups of B per block, MS chunk steps in flight per warp.  The library runs
+// <16, 4, 2>: 32 rows of B per block, one CTA per SM.  A lane has eight 16-byte loads in flight, a warp covers
+// WARPS x MS x 128 elements of K per round, and there is one output per thread (16 tokens x 8 RG rows of B = 32 WARPS).
+// (Measured and not kept: <8, 2, 4>, half-size CTAs two per SM, meant to overlap the rounds of a B that needs several;
+// 16 x 11008 x 4096 10.9 us against 10.2 us for the one-CTA form, 16 x 4096 x 4096 6.0 against 4.9 us.)
+template <int WARPS, int RG, int MS>
+struct RmmaCfg {
+    static_assert(WARPS == 4 * RG, "one output per thread");
+    static constexpr int kWarps = WARPS;
+    static constexpr int kThreads = WARPS * 32;
+    static constexpr int kRowGroups = RG;        // 8-row groups of B per block
+    static constexpr int kRowsPerCta = 8 * RG;
+    static constexpr int kMaxSteps = MS;         // chunk steps a warp keeps in flight at once
+    static constexpr int kRedBytes = WARPS * RG * 32 * 4 * 4;  // one 16 x (8 RG) int32 partial tile per warp
+    static constexpr int kCtasPerSm = WARPS == 16 ? 1 : 2;
+};
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
 {
@@ -45,10 +55,14 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 
 __device__ __forceinline__ uint32_t word(const uint4 &v, int s) { return s == 0 ? v.x : (s == 1 ? v.y : (s == 2 ? v.z : v.w)); }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int WARPS, int RG, int MS>
+__global__ void __launch_bounds__(WARPS * 32, (WARPS == 16 ? 1 : 2))
 gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
                  uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
 {
+    using Cfg = RmmaCfg<WARPS, RG, MS>;
+    constexpr int kWarps = Cfg::kWarps, kThreads = Cfg::kThreads, kRowGroups = Cfg::kRowGroups, kRowsPerCta = Cfg::kRowsPerCta,
+                  kMaxSteps = Cfg::kMaxSteps;
     extern __shared__ uint4 smem_u4[];
     uint4 *a_cv = smem_u4;  // [16 rows][chunks][2]: even x 16, odd x 16; rows 16 bytes longer than their data so that the two
                             // rows a quarter-warp reads at once fall on different banks
@@ -136,7 +150,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
 #pragma unroll
             for (int j = 0; j < 4; ++j) red[((warp * kRowGroups + rg) * 4 + j) * 32 + ((lane + 4 * (2 * rg + (j & 1))) & 31)] = d[rg][j];
         __syncthreads();
-        const int tok = threadIdx.x >> 5, col = threadIdx.x & 31;  // 16 tokens x 32 rows of B
+        const int tok = threadIdx.x / kRowsPerCta, col = threadIdx.x % kRowsPerCta;  // 16 tokens x kRowsPerCta rows of B
         const int rg = col >> 3, cc = col & 7;
         // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
         const int src_lane = (tok & 7) * 4 + (cc >> 1);
@@ -208,22 +222,24 @@ bool rmma_eligible(const GemmArgs &g)
            (reinterpret_cast<uintptr_t>(g.B) & 15u) == 0;
 }
 
-int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
+template <int WARPS, int RG, int MS>
+static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 {
-    if (!rmma_eligible(g)) return QM_ERR_ARG;
-    const size_t smem = (size_t)16 * (g.k + 16) + kRedBytes;  // rows of A are padded by 16 bytes
+    using Cfg = RmmaCfg<WARPS, RG, MS>;
+    auto kernel = gemm_rmma_kernel<WARPS, RG, MS>;
+    const size_t smem = (size_t)16 * (g.k + 16) + Cfg::kRedBytes;  // rows of A are padded by 16 bytes
     static bool configured[64] = {false};
     if (!configured[ctx.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_rmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (kRmmaMaxK + 16) + kRedBytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (kRmmaMaxK + 16) + Cfg::kRedBytes);
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
         configured[ctx.device & 63] = true;
     }
-    const int blocks = (g.n + kRowsPerCta - 1) / kRowsPerCta;
+    const int blocks = (g.n + Cfg::kRowsPerCta - 1) / Cfg::kRowsPerCta;
     const int sms = ctx.num_sms > 0 ? ctx.num_sms : 1;
-    const int per_sm = smem <= 100 * 1024 ? 2 : 1;  // register file: 512 threads x up to 64 registers fit twice
+    const int slots = sms * ((Cfg::kCtasPerSm == 2 && 2 * (smem + 1024) <= 227 * 1024) ? 2 : 1);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(blocks < sms * per_sm ? blocks : sms * per_sm), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.gridDim = dim3((unsigned)(blocks < slots ? blocks : slots), 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
     cudaLaunchAttribute attr[1];
@@ -235,10 +251,16 @@ int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_rmma_kernel, g.A, g.B, g.C, g.ldc, g.m, g.n, g.k, static_cast<uint16_t *>(g.out_bf16),
-                                       g.scale_a, g.scale_b);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, g.A, g.B, g.C, g.ldc, g.m, g.n, g.k, static_cast<uint16_t *>(g.out_bf16), g.scale_a,
+                                       g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_rmma_kernel launch");
     return QM_OK;
+}
+
+int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    if (!rmma_eligible(g)) return QM_ERR_ARG;
+    return rmma_launch_cfg<16, 4, 2>(g, ctx);
 }
 
 }  // namespace qm

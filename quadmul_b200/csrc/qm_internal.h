@@ -106,15 +106,16 @@ constexpr int kRmmaMaxK = 8192;  // 16 converted rows of A (16 * K bytes) + 32 K
 constexpr int kRmmaMaxRows = 64;       // rows of A, in tiles of 16 that pass through shared memory one after the other
 constexpr int kRmmaMaxKTiled = 4096;   // ... which needs a block's weights resident in registers (16 warps x 2 steps x 128 elements)
 // Shapes the table gives it: 3 to 16 rows of A (one or two go to the row kernel) and a B whose 32-row blocks fit the SMs in at
-// most two rounds (16 x 4096 x 4096: 4.7 us against 8.2 us on the TMA/TMEM decode kernel; 16 x 8192 x 4096: 9.4 against 9.8 us).
-// Rounds of one CTA do not overlap, so beyond that the decode kernel is faster (16 x 11008 x 4096: 11.4 against 10.5 us).
+// most three rounds (16 x 4096 x 4096: 4.9 us against 8.2 us on the TMA/TMEM decode kernel; 16 x 8192 x 4096: 7.7 against 9.8 us;
+// 16 x 11008 x 4096: 10.2 against 10.5 us).  Rounds of one CTA do not overlap, so beyond that the decode kernel is faster
+// (16 x 28672 x 4096: 19.8 against 16.0 us).
 // A second 16-row tile of A re-uses the weights in registers and costs ~2.5 us more (32 x 4096 x 4096: 7.4 us against 9.4 us on the
 // decode kernel); with three or four tiles the decode kernel is level or ahead (64 x 4096 x 4096: 12.5 against 11.8 us).
 inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
 {
     if (m < 3 || k % 32 != 0) return false;
     const int blocks = (n + 31) / 32;
-    if (m <= 16) return k <= kRmmaMaxK && blocks <= 2 * num_sms;
+    if (m <= 16) return k <= kRmmaMaxK && blocks <= 3 * num_sms;
     return m <= 32 && k <= kRmmaMaxKTiled && blocks <= num_sms;
 }
 bool rmma_eligible(const GemmArgs &g);  // limits of the kernel itself (m <= 16, k <= kRmmaMaxK, any n) and 16-byte-aligned A and B
