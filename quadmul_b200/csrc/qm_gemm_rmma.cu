@@ -33,7 +33,8 @@ namespace {
 // <16, 4, 2>: 32 rows of B per block, one CTA per SM.  A lane has eight 16-byte loads in flight, a warp covers
 // WARPS x MS x 128 elements of K per round, and there is one output per thread (16 tokens x 8 RG rows of B = 32 WARPS).
 // (Measured and not kept: <8, 2, 4>, half-size CTAs two per SM, meant to overlap the rounds of a B that needs several;
-// 16 x 11008 x 4096 10.9 us against 10.2 us for the one-CTA form, 16 x 4096 x 4096 6.0 against 4.9 us.)
+// 16 x 11008 x 4096 10.9 us against 10.2 us for the one-CTA form, 16 x 4096 x 4096 6.0 against 4.9 us; and issuing the next
+// block's loads before the reduction of the current one instead of prefetching it to L2: 10.9 against 10.2 us.)
 template <int WARPS, int RG, int MS>
 struct RmmaCfg {
     static_assert(WARPS == 4 * RG, "one output per thread");
