@@ -1,4 +1,4 @@
-// Packed-int4 GEMM for up to 16 rows of A on small weight matrices: register-resident decode kernel.
+// Packed-int4 GEMM for up to 64 rows of A (in tiles of 16) on small weight matrices: register-resident decode kernel.
 //
 // Same contract as the other GEMM kernels (exact int32 C = A * B^T on nibbles; replaces the reference's igemm<Config>,
 // kernel.cu:62-266).  At the decode sizes named for this library (16 x 4096 x 4096, 16 x 11008 x 4096: 8-23 MB of weights,
@@ -71,7 +71,12 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     const int a_stride = 2 * chunks + 1;  // in 16-byte units
     // [warp][row group][j][32]: accumulator register j of lane l at position (l + 4 (2 rg + (j & 1))) % 32, which makes both the
     // writes (one register of all lanes) and the reads (one token, 32 rows of B) hit 32 different banks
-    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * a_stride);
+    // More than 16 rows of A: all rows stay PACKED in shared memory (row pitch chunks + 4 units, so that two neighbouring rows
+    // fall on different banks) and the fragments are split on the fly; nothing is converted or re-read per 16-row tile.
+    const int tiles = (m + 15) / 16;  // token tiles of 16 rows of A
+    const int pk_stride = chunks + 4;
+    const size_t a_units = tiles > 1 ? (size_t)16 * tiles * pk_stride : (size_t)16 * a_stride;
+    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + a_units);
     const int64_t row_bytes = k / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -104,6 +109,16 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             tc::split_s4x32(v, lo, hi);
             a_cv[r * a_stride + 2 * c] = lo;
             a_cv[r * a_stride + 2 * c + 1] = hi;
+        }
+        __syncthreads();
+    };
+    // all rows of A, packed as they are, -> shared memory (zero beyond m); all threads, followed by a barrier
+    auto copy_a_packed = [&]() {
+        for (int i = threadIdx.x; i < 16 * tiles * chunks; i += kThreads) {
+            const int r = i / chunks, c = i - r * chunks;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + (int64_t)r * row_bytes) + c);
+            a_cv[r * pk_stride + c] = v;
         }
         __syncthreads();
     };
@@ -144,6 +159,32 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             }
         }
     };
+    // the same for token tile tt of the packed rows of A: the fragments are split here
+    auto mma_round_packed = [&](int(&d)[kRowGroups][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0, int tt) {
+#pragma unroll
+        for (int u = 0; u < kMaxSteps; ++u) {
+            const int t = t0 + u * kWarps;
+            const int c = 4 * t + q;
+            if (t < steps) {  // uniform over the warp
+                uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
+                if (c < chunks) {
+                    p0 = a_cv[(16 * tt + g) * pk_stride + c];
+                    p1 = a_cv[(16 * tt + g + 8) * pk_stride + c];
+                }
+                uint4 alo0, ahi0, alo1, ahi1;
+                tc::split_s4x32(p0, alo0, ahi0);
+                tc::split_s4x32(p1, alo1, ahi1);
+#pragma unroll
+                for (int rg = 0; rg < kRowGroups; ++rg) {
+                    uint4 wl, wh;
+                    tc::split_s4x32(w[u][rg], wl, wh);
+#pragma unroll
+                    for (int s = 0; s < 4; ++s)
+                        mma_s8(d[rg], word(alo0, s), word(alo1, s), word(ahi0, s), word(ahi1, s), word(wl, s), word(wh, s));
+                }
+            }
+        }
+    };
     // partial tiles of all warps -> shared memory -> one output per thread (token tile tt, block rb); two barriers
     auto reduce_store = [&](const int(&d)[kRowGroups][4], int rb, int tt) {
 #pragma unroll
@@ -172,7 +213,6 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         __syncthreads();  // `red` and the rows of A are rewritten next
     };
 
-    const int tiles = (m + 15) / 16;                       // token tiles of 16 rows of A
     const bool resident = steps <= kWarps * kMaxSteps;     // a block's weights fit one round of registers (the host requires it for tiles > 1)
     bool a_ready = false;
     for (int rb = blockIdx.x; rb < num_blocks; rb += gridDim.x) {
@@ -182,16 +222,18 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             // the weights stay in registers while the token tiles pass through shared memory one after the other
             load_round(w, rb, warp);
             prefetch_block(rb + (int)gridDim.x);  // the next block goes to L2 meanwhile
+            if (!a_ready) {
+                if (tiles > 1) copy_a_packed();
+                else convert_a(0);
+                a_ready = true;
+            }
             for (int tt = 0; tt < tiles; ++tt) {
-                if (tiles > 1 || !a_ready) {
-                    convert_a(tt);
-                    a_ready = true;
-                }
 #pragma unroll
                 for (int rg = 0; rg < kRowGroups; ++rg)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) d[rg][j] = 0;
-                mma_round(d, w, warp);
+                if (tiles > 1) mma_round_packed(d, w, warp, tt);
+                else mma_round(d, w, warp);
                 reduce_store(d, rb, tt);
             }
         } else {
@@ -228,10 +270,15 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 {
     using Cfg = RmmaCfg<WARPS, RG, MS>;
     auto kernel = gemm_rmma_kernel<WARPS, RG, MS>;
-    const size_t smem = (size_t)16 * (g.k + 16) + Cfg::kRedBytes;  // rows of A are padded by 16 bytes
+    const int tiles = (g.m + 15) / 16;
+    // 16 converted rows of A padded by 16 bytes, or (more than 16 rows) all rows packed and padded by 64 bytes
+    const size_t smem = (tiles > 1 ? (size_t)16 * tiles * (g.k / 2 + 64) : (size_t)16 * (g.k + 16)) + Cfg::kRedBytes;
     static bool configured[64] = {false};
     if (!configured[ctx.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (kRmmaMaxK + 16) + Cfg::kRedBytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (16 * (kRmmaMaxK + 16) > kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64) ? 16 * (kRmmaMaxK + 16)
+                                                                                                                 : kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64)) +
+                                                 Cfg::kRedBytes);
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
         configured[ctx.device & 63] = true;
     }

@@ -109,14 +109,15 @@ constexpr int kRmmaMaxKTiled = 4096;   // ... which needs a block's weights resi
 // most three rounds (16 x 4096 x 4096: 4.9 us against 8.2 us on the TMA/TMEM decode kernel; 16 x 8192 x 4096: 7.7 against 9.8 us;
 // 16 x 11008 x 4096: 10.2 against 10.5 us).  Rounds of one CTA do not overlap, so beyond that the decode kernel is faster
 // (16 x 28672 x 4096: 19.8 against 16.0 us).
-// A second 16-row tile of A re-uses the weights in registers and costs ~2.5 us more (32 x 4096 x 4096: 7.4 us against 9.4 us on the
-// decode kernel); with three or four tiles the decode kernel is level or ahead (64 x 4096 x 4096: 12.5 against 11.8 us).
+// Further 16-row tiles of A re-use the weights in registers and cost ~1.5 us each (32 x 4096 x 4096: 5.6 us, 64 x 4096 x 4096:
+// 8.6 us, against 9.4 and 11.8 us on the decode kernel; 32 x 8192 x 4096, two rounds: 9.4 against 10.7 us).
 inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
 {
     if (m < 3 || k % 32 != 0) return false;
     const int blocks = (n + 31) / 32;
     if (m <= 16) return k <= kRmmaMaxK && blocks <= 3 * num_sms;
-    return m <= 32 && k <= kRmmaMaxKTiled && blocks <= num_sms;
+    if (m <= 32) return k <= kRmmaMaxKTiled && blocks <= 2 * num_sms;
+    return m <= kRmmaMaxRows && k <= kRmmaMaxKTiled && blocks <= num_sms;
 }
 bool rmma_eligible(const GemmArgs &g);  // limits of the kernel itself (m <= 16, k <= kRmmaMaxK, any n) and 16-byte-aligned A and B
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx);

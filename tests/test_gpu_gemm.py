@@ -131,7 +131,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
 @pytest.mark.parametrize("m,n,k,expect", [
     (16, 4096, 16384, dict(tile_n=16, split_k=4, stream_k=1, ctas_per_sm=1)),     # K partitions through scratch (K above the register kernel's limit)
     (32, 4096, 8192, dict(tile_n=32, split_k=4, stream_k=3, ctas_per_sm=1)),      # ... as one cluster
-    (64, 4096, 4096, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
+    (64, 4096, 8192, dict(tile_n=64, split_k=4, stream_k=3, ctas_per_sm=1)),
     (8, 11008, 8448, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM (K above the register kernel's limit)
     (64, 11008, 4096, dict(tile_n=64, split_k=1, ctas_per_sm=1)),
     (16, 28672, 8192, dict(tile_n=16, split_k=1, stream_k=1, ctas_per_sm=2)),     # 224 tiles on 296 CTA slots
@@ -461,7 +461,8 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     (4096, 4096, 4096, 300, dict(kernel=1, tile_n=128, swap_ab=1, cta_pair=1)),  # single-CTA tile of the general kernel
     (16, 11008, 4096, 1500, {}),                                              # register-resident kernel, three rounds of blocks
     (16, 11008, 8448, 800, {}),                                               # decode kernel, two CTAs per SM
-    (64, 4096, 4096, 1500, {}),                                               # decode kernel, cluster reduction
+    (64, 4096, 4096, 1500, {}),                                               # register-resident kernel, four tiles of A
+    (64, 4096, 8192, 800, {}),                                                # decode kernel, cluster reduction
     (1, 11008, 4096, 1500, {}),                                               # dp4a row kernel
     (16, 4096, 4096, 1500, {}),                                               # register-resident mma.sync kernel
     (16, 4096, 16384, 800, {}),                                               # decode kernel, K partitions through scratch
