@@ -115,9 +115,7 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
     const bool eligible = tc_eligible(g);
     if (kernel == QM_KERNEL_TC && !eligible) return QM_ERR_ALIGN;
     if (kernel == QM_KERNEL_GEMV && !gemv_eligible(g)) return m > kGemvMaxRows ? QM_ERR_ARG : QM_ERR_ALIGN;
-    // one to four rows of A stream the weights through dp4a: faster than the tensor path's pipeline (1 x 4096 x 4096:
-    // see qm_tile_table.h)
-    if (kernel == QM_KERNEL_AUTO && m <= 2 && gemv_eligible(g) && gemv_shape_ok(m, n, k)) kernel = QM_KERNEL_GEMV;
+    // small decode shapes: the register-resident kernel, else (one to four rows) the dp4a row kernel; rules in qm_internal.h
     if (kernel == QM_KERNEL_AUTO && rmma_eligible(g) && rmma_shape_ok(m, n, k, ctx->num_sms)) return rmma_launch(g, *ctx);
     if (kernel == QM_KERNEL_AUTO && gemv_eligible(g) && gemv_shape_ok(m, n, k)) kernel = QM_KERNEL_GEMV;
     if (kernel == QM_KERNEL_AUTO) kernel = eligible ? QM_KERNEL_TC : QM_KERNEL_SIMT;
@@ -283,7 +281,6 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
         g.out_bf16 = out_bf16, g.scale_a = scale_a, g.scale_b = scale_b;
         const TcPlan p = plan_tc(m, n, k, ctx->num_sms);
         // fused: the large-shape, the decode and the dp4a row kernel convert inside their epilogues and never write the int32 matrix
-        if (m <= 2 && gemv_eligible(g) && gemv_shape_ok(m, n, k)) return gemv_launch(g, *ctx);
         if (rmma_eligible(g) && rmma_shape_ok(m, n, k, ctx->num_sms)) return rmma_launch(g, *ctx);
         if (gemv_eligible(g) && gemv_shape_ok(m, n, k)) return gemv_launch(g, *ctx);
         if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
@@ -472,8 +469,7 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
         return QM_OK;
     }
     TcPlan p = plan_tc(m, n, k, 148);
-    opts->kernel = (m <= 2 && gemv_shape_ok(m, n, k)) ? QM_KERNEL_GEMV
-                   : rmma_shape_ok(m, n, k, 148)      ? QM_KERNEL_RMMA
+    opts->kernel = rmma_shape_ok(m, n, k, 148)        ? QM_KERNEL_RMMA
                    : gemv_shape_ok(m, n, k)           ? QM_KERNEL_GEMV
                                                       : QM_KERNEL_TC;
     opts->tile_n = p.tile_n;

@@ -6,11 +6,13 @@
 // the weights come from HBM or from L2.  This kernel has no pipeline to fill: a CTA owns 32 rows of B, its 16 warps split
 // K between them, and every lane asks for ALL of its weights (up to eight 16-byte loads) before anything else happens, so
 // the whole 64 KB block of a CTA is in flight after a few instructions and the launch is one memory round trip long.
-// While the loads fly the CTA converts the rows of A into shared memory (even elements x 16, odd elements x 16 per
-// 16-byte chunk, as everywhere in this library).  The products run on the warp-level tensor path,
-// mma.sync.m16n8k32.s8 (2048 MAC per clock and SM measured on B200, a quarter of tcgen05 but four times what 16 tokens
-// at HBM rate need): A fragment = 16 tokens x 32 K from shared memory, B fragment = 8 rows of B x 32 K straight from
-// the registers the weights were loaded into, after the same x16 split.  Lane (g, q) of a warp (g = lane / 4, q = lane % 4)
+// While the loads fly the CTA copies the rows of A, packed as they are, into shared memory.  The products run on the
+// warp-level tensor path, mma.sync.m16n8k32.s8 (2048 MAC per clock and SM measured on B200, a quarter of tcgen05 but four
+// times what 16 tokens at HBM rate need): A fragment = 16 tokens x 32 K read from shared memory and split there and then
+// into even elements x 16 and odd elements x 16 (as everywhere in this library), B fragment = 8 rows of B x 32 K straight
+// from the registers the weights were loaded into, after the same split.  (Converting A once into shared memory instead
+// cost more than it saved: 16 x 4096 x 4096 4.8 us against 3.9 us.)  Rows of A beyond 16 are further tiles that take
+// their turn against the same weight registers (K <= 4096).  Lane (g, q) of a warp (g = lane / 4, q = lane % 4)
 // loads chunk 4 t + q of row g of each of four 8-row groups, and for mma step s = 0..3 supplies word s of the even half as
 // the fragment's k = 4q..4q+3 and word s of the odd half as k = 16+4q..16+4q+3; the A fragment is built from the same
 // words of the same chunks, so every product pairs equal K indices.  The 16 partial 16 x 32 tiles of a CTA meet in shared
@@ -65,18 +67,15 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     constexpr int kWarps = Cfg::kWarps, kThreads = Cfg::kThreads, kRowGroups = Cfg::kRowGroups, kRowsPerCta = Cfg::kRowsPerCta,
                   kMaxSteps = Cfg::kMaxSteps;
     extern __shared__ uint4 smem_u4[];
-    uint4 *a_cv = smem_u4;  // [16 rows][chunks][2]: even x 16, odd x 16; rows 16 bytes longer than their data so that the two
-                            // rows a quarter-warp reads at once fall on different banks
+    // The rows of A stay PACKED in shared memory, [16 tiles rows][chunks + 4] 16-byte units (the 64 bytes of padding put the two
+    // rows a quarter-warp reads at once on different banks); the A fragments are split when they are read.
+    uint4 *a_pk = smem_u4;
     const int chunks = k / 32;
-    const int a_stride = 2 * chunks + 1;  // in 16-byte units
-    // [warp][row group][j][32]: accumulator register j of lane l at position (l + 4 (2 rg + (j & 1))) % 32, which makes both the
-    // writes (one register of all lanes) and the reads (one token, 32 rows of B) hit 32 different banks
-    // More than 16 rows of A: all rows stay PACKED in shared memory (row pitch chunks + 4 units, so that two neighbouring rows
-    // fall on different banks) and the fragments are split on the fly; nothing is converted or re-read per 16-row tile.
     const int tiles = (m + 15) / 16;  // token tiles of 16 rows of A
     const int pk_stride = chunks + 4;
-    const size_t a_units = tiles > 1 ? (size_t)16 * tiles * pk_stride : (size_t)16 * a_stride;
-    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + a_units);
+    // [warp][row group][j][32]: accumulator register j of lane l at position (l + 4 (2 rg + (j & 1))) % 32, which makes both the
+    // writes (one register of all lanes) and the reads (one token, 32 rows of B) hit 32 different banks
+    int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * tiles * pk_stride);
     const int64_t row_bytes = k / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -99,26 +98,13 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     prefetch_block((int)blockIdx.x);
     ptx::grid_dependency_wait();  // nothing above read or wrote global memory
 
-    // rows 16 tt .. 16 tt + 15 of A -> shared memory (zero beyond m); all threads, followed by a barrier
-    auto convert_a = [&](int tt) {
-        for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
-            const int r = i / chunks, c = i - r * chunks;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (16 * tt + r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + (int64_t)(16 * tt + r) * row_bytes) + c);
-            uint4 lo, hi;
-            tc::split_s4x32(v, lo, hi);
-            a_cv[r * a_stride + 2 * c] = lo;
-            a_cv[r * a_stride + 2 * c + 1] = hi;
-        }
-        __syncthreads();
-    };
     // all rows of A, packed as they are, -> shared memory (zero beyond m); all threads, followed by a barrier
     auto copy_a_packed = [&]() {
         for (int i = threadIdx.x; i < 16 * tiles * chunks; i += kThreads) {
             const int r = i / chunks, c = i - r * chunks;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < m) v = __ldg(reinterpret_cast<const uint4 *>(A + (int64_t)r * row_bytes) + c);
-            a_cv[r * pk_stride + c] = v;
+            a_pk[r * pk_stride + c] = v;
         }
         __syncthreads();
     };
@@ -136,30 +122,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             }
         }
     };
-    // d += (16 rows of A in shared memory) x (the weights of one round)
-    auto mma_round = [&](int(&d)[kRowGroups][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0) {
-#pragma unroll
-        for (int u = 0; u < kMaxSteps; ++u) {
-            const int t = t0 + u * kWarps;
-            const int c = 4 * t + q;
-            if (t < steps) {  // uniform over the warp
-                uint4 alo0 = make_uint4(0, 0, 0, 0), ahi0 = alo0, alo1 = alo0, ahi1 = alo0;
-                if (c < chunks) {
-                    alo0 = a_cv[g * a_stride + 2 * c], ahi0 = a_cv[g * a_stride + 2 * c + 1];
-                    alo1 = a_cv[(g + 8) * a_stride + 2 * c], ahi1 = a_cv[(g + 8) * a_stride + 2 * c + 1];
-                }
-#pragma unroll
-                for (int rg = 0; rg < kRowGroups; ++rg) {
-                    uint4 wl, wh;
-                    tc::split_s4x32(w[u][rg], wl, wh);
-#pragma unroll
-                    for (int s = 0; s < 4; ++s)
-                        mma_s8(d[rg], word(alo0, s), word(alo1, s), word(ahi0, s), word(ahi1, s), word(wl, s), word(wh, s));
-                }
-            }
-        }
-    };
-    // the same for token tile tt of the packed rows of A: the fragments are split here
+    // d += (token tile tt of the packed rows of A in shared memory, split here) x (the weights of one round)
     auto mma_round_packed = [&](int(&d)[kRowGroups][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0, int tt) {
 #pragma unroll
         for (int u = 0; u < kMaxSteps; ++u) {
@@ -168,8 +131,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             if (t < steps) {  // uniform over the warp
                 uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
                 if (c < chunks) {
-                    p0 = a_cv[(16 * tt + g) * pk_stride + c];
-                    p1 = a_cv[(16 * tt + g + 8) * pk_stride + c];
+                    p0 = a_pk[(16 * tt + g) * pk_stride + c];
+                    p1 = a_pk[(16 * tt + g + 8) * pk_stride + c];
                 }
                 uint4 alo0, ahi0, alo1, ahi1;
                 tc::split_s4x32(p0, alo0, ahi0);
@@ -223,8 +186,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             load_round(w, rb, warp);
             prefetch_block(rb + (int)gridDim.x);  // the next block goes to L2 meanwhile
             if (!a_ready) {
-                if (tiles > 1) copy_a_packed();
-                else convert_a(0);
+                copy_a_packed();
                 a_ready = true;
             }
             for (int tt = 0; tt < tiles; ++tt) {
@@ -232,8 +194,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 for (int rg = 0; rg < kRowGroups; ++rg)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) d[rg][j] = 0;
-                if (tiles > 1) mma_round_packed(d, w, warp, tt);
-                else mma_round(d, w, warp);
+                mma_round_packed(d, w, warp, tt);
                 reduce_store(d, rb, tt);
             }
         } else {
@@ -245,10 +206,10 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 load_round(w, rb, t0);
                 if (t0 == warp) prefetch_block(rb + (int)gridDim.x);
                 if (!a_ready) {  // every warp has at least one round here (steps > kWarps * kMaxSteps)
-                    convert_a(0);
+                    copy_a_packed();
                     a_ready = true;
                 }
-                mma_round(d, w, t0);
+                mma_round_packed(d, w, t0, 0);
             }
             reduce_store(d, rb, 0);
         }
@@ -271,14 +232,11 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
     using Cfg = RmmaCfg<WARPS, RG, MS>;
     auto kernel = gemm_rmma_kernel<WARPS, RG, MS>;
     const int tiles = (g.m + 15) / 16;
-    // 16 converted rows of A padded by 16 bytes, or (more than 16 rows) all rows packed and padded by 64 bytes
-    const size_t smem = (tiles > 1 ? (size_t)16 * tiles * (g.k / 2 + 64) : (size_t)16 * (g.k + 16)) + Cfg::kRedBytes;
+    const size_t smem = (size_t)16 * tiles * (g.k / 2 + 64) + Cfg::kRedBytes;  // packed rows of A, padded by 64 bytes
     static bool configured[64] = {false};
     if (!configured[ctx.device & 63]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (16 * (kRmmaMaxK + 16) > kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64) ? 16 * (kRmmaMaxK + 16)
-                                                                                                                 : kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64)) +
-                                                 Cfg::kRedBytes);
+                                             kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64) + Cfg::kRedBytes);  // also covers 16 rows at kRmmaMaxK
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
         configured[ctx.device & 63] = true;
     }

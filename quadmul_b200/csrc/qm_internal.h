@@ -105,17 +105,18 @@ int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx);
 constexpr int kRmmaMaxK = 8192;  // 16 converted rows of A (16 * K bytes) + 32 KB of partial tiles fit in shared memory
 constexpr int kRmmaMaxRows = 64;       // rows of A, in tiles of 16 that pass through shared memory one after the other
 constexpr int kRmmaMaxKTiled = 4096;   // ... which needs a block's weights resident in registers (16 warps x 2 steps x 128 elements)
-// Shapes the table gives it: 3 to 16 rows of A (one or two go to the row kernel) and a B whose 32-row blocks fit the SMs in at
-// most three rounds (16 x 4096 x 4096: 4.9 us against 8.2 us on the TMA/TMEM decode kernel; 16 x 8192 x 4096: 7.7 against 9.8 us;
-// 16 x 11008 x 4096: 10.2 against 10.5 us).  Rounds of one CTA do not overlap, so beyond that the decode kernel is faster
-// (16 x 28672 x 4096: 19.8 against 16.0 us).
-// Further 16-row tiles of A re-use the weights in registers and cost ~1.5 us each (32 x 4096 x 4096: 5.6 us, 64 x 4096 x 4096:
-// 8.6 us, against 9.4 and 11.8 us on the decode kernel; 32 x 8192 x 4096, two rounds: 9.4 against 10.7 us).
+// Shapes the table gives it, from sweeps on B200 (us per launch, this kernel against the next best):
+//   up to 16 rows of A, K <= 8192: while the 32-row blocks of B fit the SMs in at most four rounds (16 x 4096 x 4096 3.9 / 8.2,
+//   16 x 11008 x 4096 9.1 / 10.5, 16 x 16384 x 4096 12.1, 16 x 8192 x 8192 11.5 / 12.4; beyond: 16 x 28672 x 4096 18.5 / 15.9);
+//   one or two rows: only one round (2 x 4096 x 4096 3.8 / 4.7 on the row kernel, which streams better beyond: 1 x 11008 x 4096 7.7);
+//   17-32 rows (K <= 4096): two rounds (32 x 4096 x 4096 5.9 / 9.4, 32 x 8192 x 4096 9.4 / 10.7, 32 x 11008 x 4096 12.8 / 12.2);
+//   33-64 rows (K <= 4096): one round (64 x 4096 x 4096 9.1 / 11.8, 64 x 8192 x 4096 14.5 / 12.9).
 inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
 {
-    if (m < 3 || k % 32 != 0) return false;
+    if (m < 1 || k % 32 != 0) return false;
     const int blocks = (n + 31) / 32;
-    if (m <= 16) return k <= kRmmaMaxK && blocks <= 3 * num_sms;
+    if (m <= 2) return k <= kRmmaMaxK && blocks <= num_sms;
+    if (m <= 16) return k <= kRmmaMaxK && blocks <= 4 * num_sms;
     if (m <= 32) return k <= kRmmaMaxKTiled && blocks <= 2 * num_sms;
     return m <= kRmmaMaxRows && k <= kRmmaMaxKTiled && blocks <= num_sms;
 }

@@ -86,10 +86,10 @@ def test_plan(qm):
     assert qm.plan(16, 11008, 16384)["ctas_per_sm"] == 2 and qm.plan(16, 11008, 16384)["split_k"] == 3  # K above the register kernel's limit
     wide = qm.plan(64, 4096, 8192)  # wide token tile (K above the register kernel's limit): K partitions as one cluster
     assert wide["stream_k"] == 3 and wide["split_k"] == 4 and wide["tile_n"] == 64
-    assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 28672, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(1, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(1, 11008, 4096)["kernel"] == _lib.QM_KERNEL_GEMV and qm.plan(5, 28672, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(4, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(4, 28672, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(16, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(16, 28672, 4096)["kernel"] == _lib.QM_KERNEL_TC
-    assert qm.plan(4, 6144, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(64, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(65, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
+    assert qm.plan(4, 4096, 16384)["kernel"] == _lib.QM_KERNEL_TC and qm.plan(64, 4096, 4096)["kernel"] == _lib.QM_KERNEL_RMMA and qm.plan(65, 4096, 4096)["kernel"] == _lib.QM_KERNEL_TC
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -105,10 +105,11 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
         for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
             for k in (32, 128, 512, 4096, 28672):
                 p = qm.plan(m, n, k)
-                blocks = (n + 31) // 32  # register-resident kernel: 32-row blocks of B, at most two rounds (one with two tiles of A)
-                rmma = (3 <= m <= 16 and k <= 8192 and blocks <= 444) or (17 <= m <= 32 and k <= 4096 and blocks <= 296) or (33 <= m <= 64 and k <= 4096 and blocks <= 148)
-                gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)              # one to four rows: dp4a row kernel
-                want = _lib.QM_KERNEL_GEMV if m <= 2 else _lib.QM_KERNEL_RMMA if rmma else _lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC
+                blocks = (n + 31) // 32  # register-resident kernel: rounds of 32-row blocks of B over 148 SMs
+                rmma = ((m <= 2 and k <= 8192 and blocks <= 148) or (3 <= m <= 16 and k <= 8192 and blocks <= 592)
+                        or (17 <= m <= 32 and k <= 4096 and blocks <= 296) or (33 <= m <= 64 and k <= 4096 and blocks <= 148))
+                gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)  # one to four rows: dp4a row kernel
+                want = _lib.QM_KERNEL_RMMA if rmma else _lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC
                 assert p["kernel"] == want
                 assert p["tile_n"] in (16, 32, 64, 128, 256)
                 swap, pair, tm = p["swap_ab"] == 2, p["cta_pair"] == 2, p["a_tmem"] == 2

@@ -157,7 +157,7 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
 
     torch = cuda_clean
     for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (7, 8192), (300, 28672), (2, 64), (16503, 256)):  # the last: four rows of B per step
-        if m <= 2:
+        if m <= 2 and n > 32 * 148:
             assert qm.plan(m, n, k)["kernel"] == _lib.QM_KERNEL_GEMV
         ap = oracle.fill_packed(m, k, 91); bp = oracle.fill_packed(n, k, 92)
         want = oracle.gemm(ap, bp)
