@@ -13,6 +13,14 @@ The line printed by rank 0 carries, beside the base keys:
   cpu_baseline  the CPU oracle timed on a bounded row slab of the same product (N=1 only)
   e2e           the same metric through the host-buffer C-ABI call, copies included
   clocks        SM clock and throttle reasons sampled during the timed region
+  verified      the C that is timed, compared with the CPU oracle before the timed region (full rows + sampled points);
+                a mismatch aborts the run without a number (the reference checks before it times, test.py:39-43)
+  extra         (1 GPU) further shapes of the target list, each verified and timed in a CUDA graph that rotates its
+                buffers past the L2: the decode shapes against the HBM roofline, the M = 2048 prefill shapes and
+                32768^3 against the tensor roofline
+  sharded_check, large   (2+ GPUs, after the timed region) the column-sharded product with the NCCL gather and with
+                the fused peer-store gather checked against the oracle on rank 0, and 32768^3 strong scaling:
+                compute only, with NCCL gather, with fused gather
 
 `--impl reference` times the reference's own CPU implementation of the path (its compiled
 cpu_gemm_int8 + unpack_int4_matrix where that build exists, else the oracle port) on the host cores.
@@ -38,8 +46,8 @@ METRIC = "int4 GEMM TOPS at M=N=K=8192"
 UNIT = "TOPS"
 INT8_PEAK_NOMINAL_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
 FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of gemm_tc2_kernel (164.6 MB + 222.1 MB),
-# from the ncu capture summarised in profiles/gemm_tc2_8192.md
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the headline kernel at 8192^3, from an ncu capture of this
+# command (`--steps 2 --warmup 3 --no-cpu-baseline --no-e2e --no-extra`, one launch captured): 164.6 MB read + 222.1 MB written
 DRAM_TRAFFIC_BYTES_PER_LAUNCH = 386.7e6
 
 
@@ -234,6 +242,231 @@ def reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+
+# ------------------------------------------------------------------------------------------
+# verification against the CPU oracle (checker only: never inside a timed region)
+# ------------------------------------------------------------------------------------------
+def verify_against_oracle(torch, a, b, c, m, n, k, seams=(), rows_full=2, points=4096, seed=1):
+    """Compare C (a device tensor [m, >= n]; its columns [0, n) hold A x B^T for the given packed device operands) with the
+    oracle: `rows_full` whole rows (first and last), `points` sampled positions with tile seams (multiples of 192 and 256,
+    and the given extra seam columns) mixed in.  Returns a description; raises SystemExit on the first difference."""
+    import numpy as np
+
+    from oracle import oracle as o
+
+    ap = a.cpu().numpy().view(np.uint8)
+    bp = b.cpu().numpy().view(np.uint8)
+    rng = np.random.default_rng(seed)
+    row_ids = sorted({0, m - 1} if rows_full >= 2 else {m // 2})
+    for r in row_ids:
+        want = o.gemm(ap[r : r + 1], bp)[0]
+        got = c[r, :n].cpu().numpy()
+        if not np.array_equal(got, want):
+            bad = np.flatnonzero(got != want)
+            raise SystemExit(f"bench.py: row {r} of the {m}x{n}x{k} product differs from the oracle at {bad.size} columns "
+                             f"(first {bad[:4].tolist()}); no number reported")
+    seam_cols = [x for step in (192, 256) for x in list(range(step - 1, n, step))[:32] + list(range(step, n, step))[:32]]
+    seam_cols += [x for x in seams if 0 <= x < n]
+    cols = np.concatenate([rng.integers(0, n, max(points - len(seam_cols), 0)), np.asarray(seam_cols, dtype=np.int64)]) if n > 0 else np.zeros(0, np.int64)
+    rows = np.concatenate([rng.integers(0, m, len(cols) - min(len(cols), 64)), np.full(min(len(cols), 64), m - 1)])
+    got = c[torch.from_numpy(rows).to(c.device), torch.from_numpy(cols).to(c.device)].cpu().numpy().astype(np.int64)
+    want = o.gemm_points(ap, bp, rows, cols)
+    if not np.array_equal(got, want):
+        bad = np.flatnonzero(got != want)
+        raise SystemExit(f"bench.py: {bad.size} of {len(cols)} sampled outputs of the {m}x{n}x{k} product differ from the oracle "
+                         f"(first at row {int(rows[bad[0]])}, column {int(cols[bad[0]])}); no number reported")
+    return {"ok": True, "full_rows": len(row_ids), "points": int(len(cols)), "against": "CPU oracle (int64 accumulate)"}
+
+
+def time_graph_of_launches(torch, qm, m, n, k, per_graph, replays):
+    """One shape through qm.gemm in a CUDA graph of `per_graph` launches over rotating operand buffers (so that a small
+    problem is streamed from HBM, not served from L2).  Returns (min, median) milliseconds per launch and the tensors of
+    buffer 0 for verification."""
+    per_launch_bytes = m * k // 2 + n * k // 2 + 4 * m * n
+    rotate = 1 if per_launch_bytes > 200e6 else min(64, int(2 * 126e6 // per_launch_bytes) + 2)
+    a = qm.fill_packed(m, k, 1002)
+    bs = [qm.fill_packed(n, k, 3002 + 17 * i) for i in range(rotate)]
+    cs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(rotate)]
+    qm.gemm(a, bs[0], cs[0], m, n, k)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(per_graph):
+            qm.gemm(a, bs[i % rotate], cs[i % rotate], m, n, k)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / per_graph)
+    times.sort()
+    return times[0], times[len(times) // 2], (a, bs[0], cs[0]), rotate
+
+
+EXTRA_SHAPES = [  # (m, n, k, kind): the decode and prefill shapes of the target list, and the large square
+    (16, 4096, 4096, "decode"), (16, 11008, 4096, "decode"), (16, 28672, 8192, "decode"),
+    (2048, 12288, 4096, "prefill"), (2048, 4096, 4096, "prefill"), (2048, 22016, 4096, "prefill"), (2048, 4096, 11008, "prefill"),
+    (32768, 32768, 32768, "large"),
+]
+
+
+def extra_legs(torch, qm) -> list:
+    """Further shapes, each verified against the oracle and then timed; not part of the headline number."""
+    out = []
+    peak_t, _ = measured_peaks()
+    peak_h, _ = measured_hbm()
+    for m, n, k, kind in EXTRA_SHAPES:
+        nbytes = m * k // 2 + n * k // 2 + 4 * m * n
+        if kind == "large" and torch.cuda.mem_get_info()[0] < 8 * 2**30:
+            continue
+        per_graph, replays = (20, 7) if kind == "decode" else ((10, 5) if kind == "prefill" else (2, 3))
+        t_min, t_med, (a, b, c), rotate = time_graph_of_launches(torch, qm, m, n, k, per_graph, replays)
+        ver = verify_against_oracle(torch, a, b, c, m, n, k, points=1024, seed=m + n + k)
+        code, where = qm.device_status()
+        if code != 0:
+            raise SystemExit(f"bench.py: in-kernel wait expired in the extra leg {m}x{n}x{k} (site {where & 0xFF}); no number reported")
+        ops = 2.0 * m * n * k
+        e = {"shape": [m, n, k], "kind": kind, "us_min": t_min * 1e3, "us_median": t_med * 1e3, "verified": ver["ok"],
+             "buffers_in_rotation": rotate, "cuda_graph_launches": per_graph}
+        if kind == "decode":
+            e.update({"bound": "hbm", "gbs": nbytes / (t_med * 1e-3) / 1e9, "frac": nbytes / (t_med * 1e-3) / 1e9 / peak_h,
+                      "algorithmic_bytes": nbytes})
+        else:
+            e.update({"bound": "tensor", "tops": ops / (t_med * 1e-3) / 1e12, "frac": ops / (t_med * 1e-3) / 1e12 / peak_t,
+                      "frac_nominal": ops / (t_med * 1e-3) / 1e12 / INT8_PEAK_NOMINAL_TOPS})
+        out.append(e)
+        del a, b, c
+        torch.cuda.empty_cache()
+    return out
+
+
+def multi_gpu_legs(torch, dist, qm, world: int, rank: int, steps: int = 2) -> dict:
+    """After the headline: (a) the column-sharded product with both gathers, checked on rank 0 against the oracle;
+    (b) 32768^3 strong scaling: compute only, with NCCL gather, with fused peer-store gather (device-timed, max over
+    ranks).  Raises SystemExit on any mismatch or in-kernel time-out."""
+    import numpy as np
+
+    from oracle import oracle as o
+    from quadmul_b200.sharded import NShardedGemm, SymmetricC
+
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, n_steps):
+        fn()  # warm
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1) / n_steps)
+
+    # ---- (a) correctness of the two gather paths on a shape whose shards are uneven and cut tiles ----
+    m, n, k = 1024, 128 * (4 * world + 3), 2048
+    sh = NShardedGemm(n, world=world, rank=rank)
+    a = qm.fill_packed(m, k, 4001)
+    b_full = qm.fill_packed(n, k, 4002)
+    b = sh.shard_of(b_full).contiguous()
+    seams = sorted({x for r in range(world) for x in (sh.ranges[r][0] - 1, sh.ranges[r][0], sh.ranges[r][0] + sh.ranges[r][1] - 1)})
+    slab = sh.local(a, b, m, k)
+    full = sh.gather(slab, m)
+    csym = SymmetricC(m, n)
+    csym.local.fill_(-3)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sh.local_into(a, b, m, k, csym, dst=0)
+    if rank == 0:
+        csym.wait_all()
+    torch.cuda.synchronize()
+    ok_local = True
+    if rank == 0:
+        ap_host = a.cpu().numpy().view(np.uint8)
+        bp_host = b_full.cpu().numpy().view(np.uint8)
+        for name, cmat in (("NCCL gather", full), ("fused peer-store gather", csym.local)):
+            verify_against_oracle(torch, a, b_full, cmat, m, n, k, seams=seams, points=4096, seed=world)
+            for col in seams:  # every shard seam as a whole column
+                want = o.gemm(ap_host, bp_host[col : col + 1])[:, 0]
+                if not np.array_equal(cmat[:, col].cpu().numpy(), want):
+                    raise SystemExit(f"bench.py: {name}: column {col} (a shard seam) differs from the oracle; no number reported")
+    else:
+        ok_local = bool((csym.local == -3).all())  # nobody may write into the other ranks' copies
+    code, where = qm.device_status()
+    flag = torch.tensor([0 if (ok_local and code == 0) else 1], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if int(flag.item()) != 0:
+        raise SystemExit("bench.py: sharded check failed on some rank (stray writes or an in-kernel time-out); no number reported")
+    result = {"sharded_check": {"ok": True, "world": world, "shape": [m, n, k], "paths": ["nccl_gather", "fused_gather"],
+                                "checked": "rank 0: 2 full rows, 4096 points and every shard-seam column against the CPU oracle, both paths"}}
+    del full, csym, slab, a, b, b_full
+    torch.cuda.empty_cache()
+
+    # ---- (b) 32768^3, B column-sharded, A replicated ----
+    m = n = k = 32768
+    sh = NShardedGemm(n, world=world, rank=rank)
+    a = qm.fill_packed(m, k, 1005)
+    b = qm.fill_packed(sh.count, k, 2005 + 7919 * rank)
+    c_local = torch.empty((m, sh.count), dtype=torch.int32, device="cuda")
+    compute_ms = timed(lambda: sh.local(a, b, m, k, out=c_local), steps + 1)
+    full_c = torch.empty((m, n), dtype=torch.int32, device="cuda")
+
+    def with_nccl():
+        sh.local(a, b, m, k, out=c_local)
+        sh.gather(c_local, m, out=full_c)
+
+    nccl_ms = timed(with_nccl, steps)
+    del full_c
+    torch.cuda.empty_cache()
+    csym = SymmetricC(m, n)
+
+    def with_fused():
+        sh.local_into(a, b, m, k, csym, dst=0)
+        if rank == 0:
+            csym.wait_all()
+
+    fused_ms = timed(with_fused, steps)
+    dist.barrier()
+    if rank == 0:  # the gathered matrix, sampled: own slab and every other rank's
+        bp_rows = {}
+        rng = np.random.default_rng(5)
+        rows = rng.integers(0, m, 512)
+        cols = np.concatenate([rng.integers(0, n, 512 - 2 * world), np.asarray([sh.ranges[r][0] for r in range(world)] + [sh.ranges[r][0] + sh.ranges[r][1] - 1 for r in range(world)])])
+        got = csym.local[torch.from_numpy(rows).cuda(), torch.from_numpy(cols).cuda()].cpu().numpy().astype(np.int64)
+        ap = a.cpu().numpy().view(np.uint8)
+        want = np.empty(len(cols), dtype=np.int64)
+        for i, (r, cidx) in enumerate(zip(rows, cols)):
+            owner = next(q for q in range(world) if sh.ranges[q][0] <= cidx < sh.ranges[q][0] + sh.ranges[q][1])
+            if owner not in bp_rows:
+                bp_rows[owner] = o.fill_packed(sh.ranges[owner][1], k, 2005 + 7919 * owner)
+            want[i] = o.gemm_points(ap[r : r + 1], bp_rows[owner][cidx - sh.ranges[owner][0] : cidx - sh.ranges[owner][0] + 1], np.zeros(1, np.int64), np.zeros(1, np.int64))[0]
+        if not np.array_equal(got, want):
+            raise SystemExit("bench.py: 32768^3 fused gather: sampled outputs on rank 0 differ from the oracle; no number reported")
+    code, where = qm.device_status()
+    flag = torch.tensor([0 if code == 0 else 1], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if int(flag.item()) != 0:
+        raise SystemExit("bench.py: in-kernel time-out in the 32768^3 legs; no number reported")
+    ops = 2.0 * m * n * k
+    result["large"] = {"shape": [m, n, k], "world": world, "scaling": "strong", "steps": steps,
+                       "compute_ms": compute_ms, "compute_tops": ops / (compute_ms * 1e-3) / 1e12,
+                       "nccl_gather_ms": nccl_ms, "fused_gather_ms": fused_ms,
+                       "note": "B column-sharded, A replicated; *_gather_ms = GEMM + bringing the full int32 C to rank 0 (NCCL: to every rank); "
+                               "fused: GEMM epilogues store into rank 0's C over NVLink, completion flags with a bounded wait; "
+                               "rank 0's gathered C sampled against the CPU oracle"}
+    del csym, a, b, c_local
+    torch.cuda.empty_cache()
+    return result
+
+
 # ------------------------------------------------------------------------------------------
 # native arm
 # ------------------------------------------------------------------------------------------
@@ -318,7 +551,8 @@ def native_arm(args) -> None:
             qm.gemm_ex(a, bs[i], cs[i], m, n_local, k, kernel=1, **forced)
         elif csym is not None:
             sh.local_into(a, bs[i], m, k, csym, dst=0)  # epilogue stores go to rank 0's C over NVLink
-            csym.barrier()
+            if rank == 0:
+                csym.wait_all()  # completion flags, bounded wait
         elif full_c is not None:
             sh.local(a, bs[i], m, k, out=cs[i])
             sh.gather(cs[i], m, out=full_c)
@@ -339,6 +573,14 @@ def native_arm(args) -> None:
             graph.replay()
     else:
         step = launch
+
+    # the C that is about to be timed, against the CPU oracle (the reference checks before it times: test.py:39-43)
+    verified = None
+    if dq is None and csym is None:
+        launch()
+        torch.cuda.synchronize()
+        counter[0] = 0
+        verified = verify_against_oracle(torch, a, bs[0], cs[0], m, n_local, k, seed=rank + 1)
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
@@ -435,6 +677,8 @@ def native_arm(args) -> None:
             "gpu_launches": gpu_launches,
             "clocks": clocks,
         }
+        if verified is not None:
+            line["verified"] = verified
 
     # ---- end to end through the host-buffer C-ABI call, copies inside the timed region ----
     if not args.no_e2e and not large:
@@ -452,6 +696,15 @@ def native_arm(args) -> None:
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         if rank == 0:
+            import numpy as np
+
+            from oracle import oracle as o
+
+            pos = np.arange(0, m * n_local, 65537, dtype=np.int64)
+            expected = int(o.gemm_points(ha.numpy().view(np.uint8), hb.numpy().view(np.uint8), pos // n_local, pos % n_local).sum())
+            checksum = int(hc.view(-1)[:: 65537].to(torch.int64).sum())
+            if checksum != expected:
+                raise SystemExit(f"bench.py: end-to-end result checksum {checksum} != {expected} (oracle); no number reported")
             line["e2e"] = {
                 "value": ops_per_launch * world / float(dt.item()) / 1e12,
                 "unit": UNIT,
@@ -460,10 +713,22 @@ def native_arm(args) -> None:
                 "ms_per_step": float(dt.item()) * 1e3,
                 "steps": e2e_steps,
                 "api": "qm_gemm_s4_host (pinned host A, B in; int32 C out; per GPU)",
-                "result_checksum": int(hc.view(-1)[:: 65537].sum()),
+                "result_checksum": checksum,
+                "result_checksum_expected": expected,
+                "result_checksum_of": f"every 65537th element of the host C ({len(pos)} elements), expected value from the CPU oracle",
             }
             line["gpu_launches"] += e2e_steps + 1
 
+    headline = not custom and not large and not forced and dq is None and args.graph == 0
+    if headline and not args.no_extra:
+        del bs, cs, c, a
+        torch.cuda.empty_cache()
+        if world == 1:
+            line["extra"] = extra_legs(torch, qm)
+        else:
+            legs = multi_gpu_legs(torch, dist, qm, world, rank)
+            if rank == 0:
+                line.update(legs)
     if rank == 0 and world == 1 and not custom and not large and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_port()
     if rank == 0:
@@ -528,6 +793,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the further shapes (1 GPU) and the sharded check / 32768^3 legs (2+ GPUs)")
     ap.add_argument("--shape", default=None, help="M,N,K of a single-GPU case other than the headline one (profiling, sweeps)")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--swap-ab", type=int, default=0)

@@ -42,7 +42,7 @@ typedef enum qm_kernel {
     QM_KERNEL_TC = 1,  /* TMA + mbarrier ring + in-smem s4->s8 + tcgen05.mma kind::i8 + TMEM   */
     QM_KERNEL_SIMT = 2, /* dp4a kernel for shapes/alignments the tensor path does not take      */
     QM_KERNEL_GEMV = 3, /* m <= 4: weight-streaming dp4a kernel (same shape limits as QM_KERNEL_TC) */
-    QM_KERNEL_RMMA = 4  /* m <= 16, k <= 8192: weights straight into registers, warp-level mma.sync s8     */
+    QM_KERNEL_RMMA = 4  /* m <= 64 (k <= 8192 for m <= 16, k <= 4096 beyond): weights straight into registers, warp-level mma.sync s8 */
 } qm_kernel_t;
 
 /* Options for qm_gemm_s4_ex.  Zero-initialise for defaults. */
@@ -84,8 +84,22 @@ int qm_init(int device);
  * (reference kernel.cu:334-385) behind `quadmul.gemm` (reference extension.cpp:8-24).  Unlike the
  * reference, every (m, n, k) with k even is accepted; shapes the tensor path cannot take
  * (k % 32 != 0, pointers not 16-byte aligned, k >= 131072) run on the dp4a kernel instead.
+ *
+ * Calls may overlap on the GPU (different streams, several host threads).  Forms that cut K keep their partial tiles and
+ * arrival counters in per-device scratch memory that qm_init allocates; every stream gets a slice of its own the first time
+ * it needs one (6 slices per device; the per-thread default stream counts once per host thread), and a call on a seventh stream
+ * runs a form without scratch instead, so results never depend on what else is running.  A launch captured into a CUDA graph
+ * keeps the slice of the stream it was captured on: graphs that are replayed at the same time must have been captured on
+ * different streams.
  */
 int qm_gemm_s4(const void *A, const void *B, void *C, int m, int n, int k, void *stream);
+
+/*
+ * Gives back the scratch slice that `stream` holds on the current device (see qm_gemm_s4), for programs that create and
+ * destroy many streams.  Call it when no work of this library is pending on the stream, e.g. before cudaStreamDestroy.
+ * A stream without a slice is not an error.  No counterpart in the reference (its kernel keeps no state).
+ */
+int qm_stream_release(void *stream);
 
 /* Same, with explicit kernel/tile choices (used by the tuner and the tests). */
 int qm_gemm_s4_ex(const void *A, const void *B, void *C, int m, int n, int k, void *stream,
@@ -145,10 +159,35 @@ int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t sl
                  void *stream);
 
 /*
+ * Completion flags for the fused gather of the column-sharded product, where every rank's GEMM stores its slab straight
+ * into the destination rank's C (qm_gemm_s4_ldc_ex with plain_stores on a peer mapping).
+ *   qm_flag_signal: in stream order (after the GEMM), a system-scope fence and a release store of `value` to *flag;
+ *     `flag` is normally a peer-mapped pointer to word `rank` of a flag array in the DESTINATION's memory.
+ *   qm_flags_wait: a kernel on the current device that polls flags[0 .. count) (count <= 64) until each has reached
+ *     `value` (values are step numbers that only grow), for at most `timeout_ms` (1 .. 60000).  If the limit expires
+ *     the kernel records QM_ERR_TIMEOUT, wait site 8, in the device status word (qm_device_status) and returns: a rank
+ *     that never signals costs the limit, it does not hang the GPU.
+ * No counterpart in the reference (it is single-GPU).
+ */
+int qm_flag_signal(int *flag, int value, void *stream);
+int qm_flags_wait(const int *flags, int count, int value, int timeout_ms, void *stream);
+
+/*
  * In-kernel wait status of the current device: *code is 0 or QM_ERR_TIMEOUT, *where identifies
- * the wait that gave up.  Synchronises the device.  `clear` != 0 resets the word.
+ * the wait that gave up.  Synchronises the device.  `clear` != 0 resets the word and zeroes the arrival
+ * counters of the split-K scratch, which a launch that gave up leaves non-zero; the C of such a launch
+ * is undefined.  Launches made through qm_gemm_s4_static_scratch report to a word of their own, see
+ * qm_static_scratch_status.  No counterpart in the reference (its kernel has no waits).
  */
 int qm_device_status(int *code, int *where, int clear);
+
+/*
+ * Test hook for the recovery path above: writes non-zero values into the first arrival counters of `stream`'s scratch
+ * slice, as a launch whose wait expired would leave them (asynchronous on `stream`; nothing waits, nothing faults).
+ * Until qm_device_status(clear = 1) has run, split-K launches on that stream sum the wrong partial tiles.  No
+ * counterpart in the reference.
+ */
+int qm_selftest_stale_counters(void *stream);
 
 /*
  * Exercises the time-out path of the kernels without a GEMM: launches one warp that waits, with the same bounded wait the
@@ -170,11 +209,24 @@ int qm_selftest_wait_timeout(void *stream);
  *   m <= 128 (tile_n = 16, 32, 64, 128 >= m), and 4 * tiles <= 4096; QM_ERR_WORKSPACE beyond it.
  *   Needs k % 32 == 0, k < 131072 and 16-byte-aligned A and B (QM_ERR_ALIGN otherwise).
  *   The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress) with
- *   that device current; make that first call outside any stream capture.
+ *   that device current; make that first call outside any stream capture.  The arrays are part of the
+ *   library's device code: the driver reserves their memory when it loads that code, which with lazy
+ *   module loading happens during this first call -- so a process whose device memory is already
+ *   exhausted sees the out-of-memory error here, as QM_ERR_CUDA, and nowhere later.
  *   Every call on a device shares the arrays: calls that overlap on the GPU race; order them.
+ *   A bounded in-kernel wait that expires is recorded in a status word that also lives in the
+ *   library's device code; read it with qm_static_scratch_status (qm_device_status allocates).
  */
 int qm_gemm_s4_static_scratch(const void *A, const void *B, void *C, int m, int n, int k, int split_k,
                               void *stream);
+
+/*
+ * In-kernel wait status of the launches made through qm_gemm_s4_static_scratch on the current device:
+ * same meaning as qm_device_status, and like that entry point it allocates nothing.  Synchronises the
+ * device.  QM_OK with *code = 0 when that entry point has not been used on this device yet.  It has no
+ * counterpart in the reference.
+ */
+int qm_static_scratch_status(int *code, int *where, int clear);
 
 /*
  * The GEMM with a fused dequantising epilogue, for W4A4 inference: out[r][c] (bfloat16, row pitch ldc elements) =

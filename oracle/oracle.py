@@ -32,6 +32,66 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
+def reference_dir() -> str | None:
+    """Where the reference's sources lie: $QUADMUL_REFERENCE_DIR, else a directory named `reference` beside this
+    repository; None where neither exists (a machine without the reference)."""
+    cand = os.environ.get("QUADMUL_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "kernel.cu")) else None
+
+
+_REF_EXT_PATH = os.path.join(_HERE, "_ref", "ext", "quadmul.so")
+
+
+def build_ref_extension(ref_dir: str | None = None) -> str | None:
+    """Compile the reference's own pybind file, extension.cpp, UNCHANGED and from where it lies, against the product
+    library: `wrapper` (declared at extension.cpp:6) resolves to libquadmul_b200.so instead of the reference's kernel.cu.
+    This is the drop-in claim put to the test: the reference's setup.py:10-13 minus its three CUDA sources plus
+    -lquadmul_b200.  Output: oracle/_ref/ext/quadmul.so (module name `quadmul`, as setup.py:8,11).  Returns the path, or
+    the existing build where the reference is absent, or None."""
+    import shutil
+    import sysconfig
+
+    ref_dir = ref_dir or reference_dir()
+    if ref_dir is None or not os.path.isfile(os.path.join(ref_dir, "extension.cpp")):
+        return _REF_EXT_PATH if os.path.exists(_REF_EXT_PATH) else None
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    pkg = os.path.join(os.path.dirname(_HERE), "quadmul_b200")
+    os.makedirs(os.path.dirname(_REF_EXT_PATH), exist_ok=True)
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    nvcc = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cuda_home = os.path.dirname(os.path.dirname(nvcc))
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-w", "-DTORCH_EXTENSION_NAME=quadmul", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(cuda_home, "include")]:
+        cmd += ["-isystem", inc]
+    cmd += [os.path.join(ref_dir, "extension.cpp"), "-o", _REF_EXT_PATH, f"-L{pkg}", "-lquadmul_b200",
+            "-Wl,-rpath,$ORIGIN/../../../quadmul_b200"]
+    for lib_dir in ce.library_paths():
+        cmd += [f"-L{lib_dir}", f"-Wl,-rpath,{lib_dir}"]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", f"-L{os.path.join(cuda_home, 'lib64')}",
+            "-lcudart"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("building the reference's extension.cpp against libquadmul_b200.so failed:\n" + res.stderr[-2000:])
+    return _REF_EXT_PATH
+
+
+def ref_extension():
+    """The module built by build_ref_extension (the reference's `quadmul` with this library behind it), or None."""
+    import importlib.util
+
+    if not os.path.exists(_REF_EXT_PATH):
+        return None
+    import torch  # noqa: F401  (the module links libtorch)
+
+    spec = importlib.util.spec_from_file_location("quadmul", _REF_EXT_PATH)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def build_ref(ref_dir: str) -> str | None:
     """Compile the reference from its own sources (only where they exist). Returns the path or None."""
     if not os.path.isdir(ref_dir):

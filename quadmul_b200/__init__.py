@@ -242,6 +242,26 @@ def selftest_wait_timeout() -> None:
     check(LIB.qm_selftest_wait_timeout(torch.cuda.current_stream().cuda_stream), "selftest_wait_timeout")
 
 
+def release_stream(stream) -> None:
+    """Give back the split-K scratch slice a torch.cuda.Stream holds on the current device (qm_stream_release); call it
+    once the stream's work is complete and before dropping the stream."""
+    check(LIB.qm_stream_release(stream.cuda_stream), "release_stream")
+
+
+def selftest_stale_counters() -> None:
+    """Leave non-zero arrival counters in the current stream's scratch slice, as a launch whose wait expired would
+    (qm_selftest_stale_counters); device_status(clear=True) must be called before the next split-K launch."""
+    torch = _torch()
+    check(LIB.qm_selftest_stale_counters(torch.cuda.current_stream().cuda_stream), "selftest_stale_counters")
+
+
+def static_scratch_status(clear: bool = True) -> tuple[int, int]:
+    """(code, where) of the launches made through qm_gemm_s4_static_scratch on the current device; allocates nothing."""
+    code, where = ctypes.c_int(0), ctypes.c_int(0)
+    check(LIB.qm_static_scratch_status(ctypes.byref(code), ctypes.byref(where), 1 if clear else 0), "static_scratch_status")
+    return code.value, where.value
+
+
 def device_status(clear: bool = True) -> tuple[int, int]:
     """(code, where) of the current device's in-kernel wait status; synchronises the device."""
     code, where = ctypes.c_int(0), ctypes.c_int(0)

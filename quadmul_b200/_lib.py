@@ -54,6 +54,11 @@ SIGNATURES = {
     "qm_gemm_s4_dequant_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp, ctypes.c_size_t, _vp]),
     "qm_gemm_s4_dequant_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i, _i64, _vp]),
     "qm_gemm_s4_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "qm_static_scratch_status": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), _i]),
+    "qm_selftest_stale_counters": (_i, [_vp]),
+    "qm_stream_release": (_i, [_vp]),
+    "qm_flag_signal": (_i, [_vp, _i, _vp]),
+    "qm_flags_wait": (_i, [_vp, _i, _i, _i, _vp]),
 }
 
 # the reference's C++ entry point `wrapper(void*, void*, void*, int, int, int, cudaStream_t)`

@@ -1,6 +1,7 @@
 // C ABI of the library (include/quadmul_b200.h): argument checks, per-device set-up, dispatch.
 // This layer stands where the reference has `wrapper` (kernel.cu:334-385) and the pybind
 // function `gemm` (extension.cpp:8-24).
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -15,9 +16,15 @@ namespace qm {
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr size_t kScratchBytes = 32u << 20;  // split-K partial tiles, per device
-constexpr int kNumCounters = 16384;
+// Split-K scratch of a device: kNumSlices independent slices of partial-tile memory and arrival counters.  Every stream
+// that launches a kernel with scratch gets a slice of its own (first come, first served), so launches that overlap on
+// the GPU from different streams never share partial tiles or counters; launches in one stream are ordered anyway.
+constexpr int kNumSlices = 6;
+constexpr size_t kSliceBytes = 32u << 20;  // partial tiles per slice
+constexpr int kSliceCounters = 8192;       // arrival counters / share flags per slice
 DeviceCtx g_ctx[kMaxDevices];
+std::atomic<bool> g_ctx_ready[kMaxDevices];  // release-stored after g_ctx[dev] is complete, acquire-loaded on the fast path
+std::atomic<uintptr_t> g_slice_key[kMaxDevices][kNumSlices];  // which stream owns a slice (0 = free)
 std::mutex g_mutex;
 thread_local std::string t_last_error;
 
@@ -38,9 +45,9 @@ int ensure_ctx(DeviceCtx **out)
     if (e != cudaSuccess) return record_cuda_error(e, "cudaGetDevice");
     if (dev < 0 || dev >= kMaxDevices) return QM_ERR_ARG;
     DeviceCtx &c = g_ctx[dev];
-    if (!c.ready) {
+    if (!g_ctx_ready[dev].load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_mutex);
-        if (!c.ready) {
+        if (!g_ctx_ready[dev].load(std::memory_order_relaxed)) {
             int major = 0, sms = 0;
             if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
                 return record_cuda_error(e, "cudaDeviceGetAttribute");
@@ -59,9 +66,9 @@ int ensure_ctx(DeviceCtx **out)
             }
             // split-K scratch: partial tiles and self-resetting arrival counters (zero between launches)
             void *scratch = nullptr, *counters = nullptr;
-            if ((e = cudaMalloc(&scratch, kScratchBytes)) == cudaSuccess &&
-                (e = cudaMalloc(&counters, kNumCounters * sizeof(int))) == cudaSuccess)
-                e = cudaMemset(counters, 0, kNumCounters * sizeof(int));
+            if ((e = cudaMalloc(&scratch, kNumSlices * kSliceBytes)) == cudaSuccess &&
+                (e = cudaMalloc(&counters, (size_t)kNumSlices * kSliceCounters * sizeof(int))) == cudaSuccess)
+                e = cudaMemset(counters, 0, (size_t)kNumSlices * kSliceCounters * sizeof(int));
             if (e != cudaSuccess) {
                 cudaFree(status);
                 cudaFree(scratch);
@@ -69,18 +76,59 @@ int ensure_ctx(DeviceCtx **out)
                 return record_cuda_error(e, "cudaMalloc/cudaMemset(split-K scratch)");
             }
             c.scratch = static_cast<int32_t *>(scratch);
-            c.scratch_bytes = kScratchBytes;
+            c.scratch_bytes = kSliceBytes;
             c.counters = static_cast<int *>(counters);
-            c.num_counters = kNumCounters;
+            c.num_counters = kSliceCounters;
             c.device = dev;
             c.cc_major = major;
             c.num_sms = sms;
             c.status = status;
             c.ready = true;
+            g_ctx_ready[dev].store(true, std::memory_order_release);
         }
     }
     *out = &c;
     return QM_OK;
+}
+
+// The scratch slice of `stream` on this device: -1 when every slice already belongs to another stream (the caller then
+// runs a form that needs no scratch).  The legacy default stream is one key whether it is passed as NULL or by its handle;
+// the per-thread default stream is a different stream in every host thread, so its key is the thread.
+uintptr_t stream_key(cudaStream_t stream)
+{
+    static thread_local char t_thread_tag;
+    if (stream == nullptr) return reinterpret_cast<uintptr_t>(cudaStreamLegacy);
+    if (stream == cudaStreamPerThread) return reinterpret_cast<uintptr_t>(&t_thread_tag);
+    return reinterpret_cast<uintptr_t>(stream);
+}
+
+int slice_of_stream(int dev, cudaStream_t stream)
+{
+    const uintptr_t key = stream_key(stream);
+    std::atomic<uintptr_t> *keys = g_slice_key[dev];
+    for (int i = 0; i < kNumSlices; ++i) {
+        uintptr_t cur = keys[i].load(std::memory_order_acquire);
+        if (cur == key) return i;
+        if (cur == 0) {
+            if (keys[i].compare_exchange_strong(cur, key, std::memory_order_acq_rel)) return i;
+            if (cur == key) return i;
+        }
+    }
+    return -1;
+}
+
+// A copy of the device context whose scratch and counters are the slice of `stream` (none: empty scratch).
+DeviceCtx ctx_for_stream(const DeviceCtx &c, cudaStream_t stream)
+{
+    DeviceCtx lc = c;
+    const int slice = slice_of_stream(c.device, stream);
+    if (slice < 0) {
+        lc.scratch = nullptr, lc.scratch_bytes = 0, lc.counters = nullptr, lc.num_counters = 0;
+    } else {
+        lc.scratch = c.scratch + (size_t)slice * (kSliceBytes / sizeof(int32_t));
+        lc.counters = c.counters + (size_t)slice * kSliceCounters;
+    }
+    return lc;
 }
 
 int check_gemm_args(const void *A, const void *B, void *C, int m, int n, int k, int64_t ldc)
@@ -145,17 +193,25 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k || opts->stream_k) p.ctas_per_sm = 1;
         if (p.ctas_per_sm == 2 && !(p.a_tmem && p.swap_ab && p.tile_n == 16)) return QM_ERR_ARG;
     }
+    // Scratch (partial tiles, arrival counters, share flags) comes from the slice of this call's stream; a form that
+    // needs none does not claim a slice.  With every slice taken by other streams the scratch is empty and the table's
+    // choice falls back to a form without it, below.
+    const bool is_dec = p.a_tmem && p.swap_ab;
+    const bool wants_scratch = is_dec ? ((p.split_k > 1 && p.stream_k != 2) || p.stream_k == 1) : (!p.a_tmem && p.split_k > 1);
+    DeviceCtx lc = *ctx;
+    if (wants_scratch) lc = ctx_for_stream(*ctx, g.stream);
+    else lc.scratch = nullptr, lc.scratch_bytes = 0, lc.counters = nullptr, lc.num_counters = 0;
     const bool through_scratch = (p.swap_ab || !p.a_tmem) && !(p.swap_ab && p.a_tmem && p.stream_k == 2);
     if (p.split_k > 1 && !(opts && opts->split_k) && through_scratch &&
-        (tc_scratch_bytes_needed(m, n, p) > ctx->scratch_bytes || tc_counters_needed(m, n, p) > ctx->num_counters))
+        (tc_scratch_bytes_needed(m, n, p) > lc.scratch_bytes || tc_counters_needed(m, n, p) > lc.num_counters))
         p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
     if (p.stream_k == 2 && p.split_k < 2) p.stream_k = 0;  // a cluster of one partition is the plain form
-    if (p.a_tmem && p.swap_ab) {
+    if (is_dec) {
         if ((p.tile_n != 16 && p.tile_n != 32 && p.tile_n != 64) || p.cta_pair != 1) return QM_ERR_ARG;
-        st = dec_launch(g, p, *ctx);
+        st = dec_launch(g, p, lc);
         if (st == QM_ERR_WORKSPACE && p.stream_k && !(opts && opts->stream_k)) {
             p.stream_k = 0, p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
-            st = dec_launch(g, p, *ctx);
+            st = dec_launch(g, p, lc);
         }
         return st;
     }
@@ -165,9 +221,9 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
             if (opts && opts->split_k) return QM_ERR_ALIGN;
             p.split_k = 1;
         }
-        return tc2_launch(g, *ctx, p.split_k);
+        return tc2_launch(g, lc, p.split_k);
     }
-    return tc_launch(g, p, *ctx);
+    return tc_launch(g, p, lc);
 }
 
 }  // namespace
@@ -286,13 +342,14 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
         if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
         if (tc_eligible(g) && p.a_tmem && p.swap_ab) {
             TcPlan q = p;
+            const DeviceCtx lc = ctx_for_stream(*ctx, s);  // scratch slice of this call's stream
             if (q.split_k > 1 && q.stream_k != 2 &&
-                (tc_scratch_bytes_needed(m, n, q) > ctx->scratch_bytes || tc_counters_needed(m, n, q) > ctx->num_counters))
+                (tc_scratch_bytes_needed(m, n, q) > lc.scratch_bytes || tc_counters_needed(m, n, q) > lc.num_counters))
                 q.split_k = 1;
-            st = dec_launch(g, q, *ctx);
+            st = dec_launch(g, q, lc);
             if (st == QM_ERR_WORKSPACE && q.stream_k == 1) {
                 q.stream_k = 0, q.split_k = 1;
-                st = dec_launch(g, q, *ctx);
+                st = dec_launch(g, q, lc);
             }
             return st;
         }
@@ -442,6 +499,22 @@ int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t sl
                           static_cast<cudaStream_t>(stream));
 }
 
+int qm_flag_signal(int *flag, int value, void *stream)
+{
+    if (!flag) return QM_ERR_NULL;
+    return flag_signal_launch(flag, value, static_cast<cudaStream_t>(stream));
+}
+
+int qm_flags_wait(const int *flags, int count, int value, int timeout_ms, void *stream)
+{
+    if (!flags) return QM_ERR_NULL;
+    if (count < 1 || count > 64 || timeout_ms < 1 || timeout_ms > 60000) return QM_ERR_ARG;
+    DeviceCtx *ctx = nullptr;
+    int st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    return flags_wait_launch(flags, count, value, timeout_ms, ctx->status, static_cast<cudaStream_t>(stream));
+}
+
 int qm_device_status(int *code, int *where, int clear)
 {
     DeviceCtx *ctx = nullptr;
@@ -454,9 +527,39 @@ int qm_device_status(int *code, int *where, int clear)
         return record_cuda_error(e, "cudaMemcpy(status)");
     if (code) *code = words[0];
     if (where) *where = words[1];
-    if (clear && (e = cudaMemset(ctx->status, 0, sizeof(words))) != cudaSuccess)
-        return record_cuda_error(e, "cudaMemset(status)");
+    if (clear) {
+        if ((e = cudaMemset(ctx->status, 0, sizeof(words))) != cudaSuccess) return record_cuda_error(e, "cudaMemset(status)");
+        // A launch whose wait expired leaves arrival counters and share flags of its K partitions non-zero (the partitions
+        // that gave up never arrive); they are self-resetting only in launches that complete.  Start the next launch clean.
+        if ((e = cudaMemset(ctx->counters, 0, (size_t)kNumSlices * kSliceCounters * sizeof(int))) != cudaSuccess)
+            return record_cuda_error(e, "cudaMemset(counters)");
+    }
     return QM_OK;
+}
+
+int qm_stream_release(void *stream)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return QM_ERR_ARG;
+    const uintptr_t key = stream_key(static_cast<cudaStream_t>(stream));
+    for (int i = 0; i < kNumSlices; ++i) {
+        uintptr_t cur = key;
+        if (g_slice_key[dev][i].compare_exchange_strong(cur, 0, std::memory_order_acq_rel)) break;
+    }
+    return QM_OK;
+}
+
+int qm_selftest_stale_counters(void *stream)
+{
+    DeviceCtx *ctx = nullptr;
+    int st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    const DeviceCtx lc = ctx_for_stream(*ctx, static_cast<cudaStream_t>(stream));
+    if (!lc.counters) return QM_ERR_WORKSPACE;
+    cudaError_t e = cudaMemsetAsync(lc.counters, 1, 256 * sizeof(int), static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? QM_OK : record_cuda_error(e, "cudaMemsetAsync(counters)");
 }
 
 int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)

@@ -39,28 +39,6 @@
 #include "qm_ptx.cuh"
 #include "qm_tc_common.cuh"
 
-// Optional per-role cycle accounting (compiled in only with -DQM_DEC_PROFILE): each role adds the cycles
-// between consecutive PROF marks to a slot; blocks 0 and 1 dump them to g_dec_prof at exit.
-#ifdef QM_DEC_PROFILE
-__device__ long long g_dec_prof[128];
-#define PROF_DECL          \
-    long long pt_[8] = {}; \
-    long long pt0_ = clock64();
-#define PROF(i)                   \
-    {                             \
-        long long n_ = clock64(); \
-        pt_[i] += n_ - pt0_;      \
-        pt0_ = n_;                \
-    }
-#define PROF_DUMP(role)                \
-    if (blockIdx.x < 2 && lane == 0)   \
-        for (int i_ = 0; i_ < 8; ++i_) g_dec_prof[(blockIdx.x * 8 + (role)) * 8 + i_] = pt_[i_];
-#else
-#define PROF_DECL
-#define PROF(i)
-#define PROF_DUMP(role)
-#endif
-
 namespace qm {
 
 namespace {
@@ -311,7 +289,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            PROF_DECL
             while (ok && work.next(w)) {
                 const int yP = (w.tile % tilesP) * kRowsP;
                 const int yQ = (w.tile / tilesP) * BN;
@@ -324,7 +301,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                         ok = false;
                         break;
                     }
-                    PROF(0)
                     const uint32_t dst = pk0 + s * Cfg::kPkStage;
                     mbar_arrive_expect_tx(pk_full(s), Cfg::kPkStage);
 #pragma unroll
@@ -333,10 +309,8 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                         tma_load_2d(dst + h * kPkSubP, &tmapP, x, yP, pk_full(s));
                         tma_load_2d(dst + kH * kPkSubP + h * Cfg::kPkSubQ, &tmapQ, x, yQ, pk_full(s));
                     }
-                    PROF(1)
                 }
             }
-            PROF_DUMP(0)
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -344,7 +318,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            PROF_DECL
             for (; ok && work.next(w); ++lt) {
                 const int buf = lt & 1;
                 const uint32_t bph = (lt >> 1) & 1u;
@@ -353,7 +326,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     *abort_flag = 1;
                     break;
                 }
-                PROF(0)
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 const int kb0 = w.kb0;
@@ -366,7 +338,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                         ok = false;
                         break;
                     }
-                    PROF(1)
                     tc_fence_after_sync();
 #pragma unroll
                     for (int h = 0; h < kH; ++h) {
@@ -377,23 +348,19 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                             umma_i8_ta1(tmem_d, ta + 8u * k4, dQ + 2u * k4, Cfg::kIdesc, (kb != kb0 || (h | k4) != 0) ? 1u : 0u);
                     }
                     umma_commit<1>(cv_empty(s));
-                    PROF(2)
                 }
                 if (ok) umma_commit<1>(acc_full(buf));
             }
-            PROF_DUMP(1)
         }
         __syncwarp();
     } else if (warp < kFirstPConvWarp) {
         // ------------------------------ epilogue ------------------------------
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
         uint32_t lt = 0;
-        PROF_DECL
         for (; work.next(w); ++lt) {
             const int tile = w.tile;
             const int buf = lt & 1;
             const uint32_t bph = (lt >> 1) & 1u;
-            PROF(2)
             if (!warp_wait<false>(acc_full(buf), bph, abort_flag, lane)) {
                 if (lane == 0) {
                     report_timeout(status, kWaitEpilogueAcc);
@@ -401,7 +368,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 }
                 break;
             }
-            PROF(0)
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
             const int row = quarter * 32 + lane;
@@ -438,7 +404,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty(buf));
-                    PROF(1)
                     const int owner = quarter % w.nparts, qi = quarter / w.nparts;
                     if (owner != w.part) {
                         const int sender = w.part < owner ? w.part : w.part - 1;
@@ -488,7 +453,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty(buf));  // the last columns are in registers
-                    PROF(1)
                 }
                 if (w.nparts == 1) {
                     put_cols(std::integral_constant<int, 8>{}, v, 0, q0 + c);
@@ -522,8 +486,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 put_cols(std::integral_constant<int, 0>{}, sum, 0, q0 + c);
             }
         }
-        PROF(2)
-        if (warp == 2) { PROF_DUMP(2) }
     } else if (warp < kFirstQConvWarp) {
         // ------------------------------ B converters: packed smem -> registers -> TMEM ------------------------------
         const int quarter = warp & 3;                 // TMEM lane quarter this warp may write
@@ -532,7 +494,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
         const uint32_t swz = (uint32_t)((r >> 1) & 3);  // 64-byte TMA swizzle: chunk ^= (row / 2) % 4
         uint32_t it = 0;
         bool ok = true;
-        PROF_DECL
         while (ok && work.next(w)) {
             for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
                 const int ps = it % SP, cs = it % SC;
@@ -545,7 +506,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(0)
                 const uint32_t src = pk0 + ps * Cfg::kPkStage + h * kPkSubP + (uint32_t)r * kPkRowBytes;
                 uint4 w[4];
 #pragma unroll
@@ -560,7 +520,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));  // the packed rows are in registers now
-                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -569,23 +528,19 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(2)
                 tc_fence_after_sync();
                 tmem_st_x32(tmem_a0 + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((cs * kH + h) * kASubCols), v);
                 tmem_st_wait();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(cv_full(cs));
-                PROF(3)
             }
         }
-        if (warp == kFirstPConvWarp) { PROF_DUMP(3) }
     } else {
         // ------------------------------ A converters: packed smem -> swizzled int8 smem ------------------------------
         const int ctid = threadIdx.x - kFirstQConvWarp * 32;
         uint32_t it = 0;
         bool ok = true;
-        PROF_DECL
         while (ok && work.next(w)) {
             for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
                 const int ps = it % SP, cs = it % SC;
@@ -598,7 +553,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(0)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -607,7 +561,6 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(2)
                 tc_fence_after_sync();
                 const uint32_t src = pk0 + ps * Cfg::kPkStage + kH * kPkSubP;  // both sub-blocks, contiguous
                 const uint32_t dst = cv0 + cs * Cfg::kCvStage;
@@ -626,14 +579,11 @@ gemm_dec_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));
-                PROF(1)
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(cv_full(cs));
-                PROF(3)
             }
         }
-        if (warp == kFirstQConvWarp) { PROF_DUMP(4) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -767,13 +717,5 @@ int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx)
     }
 #undef QM_DEC_ARGS
 }
-
-#ifdef QM_DEC_PROFILE
-extern "C" int qm_debug_dec_profile(long long *out64)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out64, g_dec_prof, sizeof(long long) * 128);
-    return e == cudaSuccess ? 0 : 4;
-}
-#endif
 
 }  // namespace qm

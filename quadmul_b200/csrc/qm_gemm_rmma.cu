@@ -20,6 +20,7 @@
 //
 // Launches chain through programmatic dependent launch; before griddepcontrol.wait a CTA only prefetches its weights into
 // L2 (no data is returned, so this is correct whatever the previous kernel writes).
+#include <atomic>
 #include <cstdlib>
 
 #include "qm_epilogue.cuh"
@@ -233,12 +234,12 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
     auto kernel = gemm_rmma_kernel<WARPS, RG, MS>;
     const int tiles = (g.m + 15) / 16;
     const size_t smem = (size_t)16 * tiles * (g.k / 2 + 64) + Cfg::kRedBytes;  // packed rows of A, padded by 64 bytes
-    static bool configured[64] = {false};
-    if (!configured[ctx.device & 63]) {
+    static std::atomic<bool> configured[64];  // set once per device; a repeated cudaFuncSetAttribute is harmless
+    if (!configured[ctx.device & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kRmmaMaxRows * (kRmmaMaxKTiled / 2 + 64) + Cfg::kRedBytes);  // also covers 16 rows at kRmmaMaxK
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(rmma shared memory)");
-        configured[ctx.device & 63] = true;
+        configured[ctx.device & 63].store(true, std::memory_order_release);
     }
     const int blocks = (g.n + Cfg::kRowsPerCta - 1) / Cfg::kRowsPerCta;
     const int sms = ctx.num_sms > 0 ? ctx.num_sms : 1;

@@ -27,6 +27,8 @@
 // teardown (TMEM is always freed).
 #include <cuda.h>
 
+#include <atomic>
+
 #include <cstdio>
 #include <cstdlib>
 
@@ -497,14 +499,16 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, int32_t *sc
     // only starts when another has finished would run its whole share of tiles alone.
     int units = ctx.num_sms / G;
     if (G == 2) {
-        static int max_pairs[64] = {0};
-        int &cached = max_pairs[ctx.device & 63];
+        // per-device cache; the value is the same whichever thread computes it, so an atomic word is enough
+        static std::atomic<int> max_pairs[64];
+        int cached = max_pairs[ctx.device & 63].load(std::memory_order_relaxed);
         if (cached == 0) {
             cfg.gridDim = dim3((unsigned)(2 * (ctx.num_sms / 2)), 1, 1);
             int n = 0;
             cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, SWAP, G>, &cfg);
             if (qe != cudaSuccess) return record_cuda_error(qe, "cudaOccupancyMaxActiveClusters");
             cached = n > 0 ? n : 1;
+            max_pairs[ctx.device & 63].store(cached, std::memory_order_relaxed);
             if (std::getenv("QM_LOG"))
                 std::fprintf(stderr, "quadmul_b200: tile_n=%d pair kernel: %d CTA pairs resident at once (%d SMs)\n", BN,
                              cached, ctx.num_sms);

@@ -25,6 +25,8 @@
 // All waits are bounded as in gemm_tc_kernel.
 #include <cuda.h>
 
+#include <atomic>
+
 #include <cstdio>
 #include <cstdlib>
 
@@ -32,28 +34,6 @@
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
 #include "qm_tc_common.cuh"
-
-// Optional per-role cycle accounting (compiled in only with -DQM_TC2_PROFILE): each role adds the
-// cycles between consecutive PROF marks to a slot; block 0 dumps them to g_tc2_prof at exit.
-#ifdef QM_TC2_PROFILE
-__device__ long long g_tc2_prof[128];
-#define PROF_DECL         \
-    long long pt_[8] = {}; \
-    long long pt0_ = clock64();
-#define PROF(i)                 \
-    {                           \
-        long long n_ = clock64(); \
-        pt_[i] += n_ - pt0_;     \
-        pt0_ = n_;               \
-    }
-#define PROF_DUMP(role)                                                    \
-    if (blockIdx.x < 2 && lane == 0)                                       \
-        for (int i_ = 0; i_ < 8; ++i_) g_tc2_prof[(blockIdx.x * 8 + (role)) * 8 + i_] = pt_[i_];
-#else
-#define PROF_DECL
-#define PROF(i)
-#define PROF_DUMP(role)
-#endif
 
 namespace qm {
 
@@ -215,7 +195,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
                 tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
@@ -230,7 +209,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         ok = false;
                         break;
                     }
-                    PROF(0)
                     const uint32_t dst = pk0 + s * Cfg::kPkStage;
                     mbar_arrive_expect_tx(pk_full(s), Cfg::kPkStage);
 #pragma unroll
@@ -239,10 +217,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         tma_load_2d(dst + h * kPkSubA, &tmapA, x, yA, pk_full(s));
                         tma_load_2d(dst + H * kPkSubA + h * kPkSubB, &tmapB, x, yB, pk_full(s));
                     }
-                    PROF(1)
                 }
             }
-            PROF_DUMP(0)
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -250,15 +226,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         if (lane == 0 && cta_rank == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            PROF_DECL
             for (int t = unit; t < num_tiles && ok; t += num_units, ++lt) {
-                PROF(3)
                 if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag)) {
                     report_timeout(status, kWaitMmaAcc);
                     *abort_flag = 1;
                     break;
                 }
-                PROF(0)
                 tc_fence_after_sync();
                 const int kb0 = kb_begin(t);
                 for (int kb = kb0, kbe = kb_end(t); kb < kbe; ++kb, ++it) {
@@ -270,7 +243,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         ok = false;
                         break;
                     }
-                    PROF(1)
                     tc_fence_after_sync();
 #pragma unroll
                     for (int h = 0; h < H; ++h) {
@@ -286,7 +258,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                         umma_commit<2>(cv_empty(s));
                         umma_commit<2>(mapa_cluster(cv_empty(s), 1));
                     }
-                    PROF(2)
                 }
                 if (ok) {
                     if constexpr (MC) {
@@ -297,7 +268,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     }
                 }
             }
-            PROF_DUMP(1)
         }
         __syncwarp();
     } else if (warp < kFirstAConvWarp) {
@@ -311,13 +281,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && ((ldc & 3) == 0);
         const uint32_t buf = epi0 + (uint32_t)((warp - 2) * kEpiBufBytes);
         bool buf_used = false;
-        PROF_DECL
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
             tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
-            PROF(2)
             const bool ok = warp_wait<false>(acc_full, lt & 1u, abort_flag, lane);
-            PROF(0)
             if (!ok) {
                 if (lane == 0) {
                     report_timeout(status, kWaitEpilogueAcc);
@@ -374,7 +341,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
-                PROF(1)
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
                 store_pair_bf16_tma(va, vb, buf, lane, &tmapC, q0 + 64, row0, sa, sb[2], sb[3]);
@@ -392,13 +358,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty, 0);
-            PROF(1)
             store(va, q0 + 64);
             store(vb, q0 + 96);
         }
         if (use_tma_store && lane == 0) tma_store_wait_all();  // the buffer must outlive the stores that read it
         __syncwarp();
-        if (warp == 2) { PROF_DUMP(2) }
     } else if (warp < kFirstBConvWarp) {
         // ------------------------------ A converters: packed smem -> registers -> TMEM ------------------------------
         const int quarter = warp & 3;
@@ -406,12 +370,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         const uint32_t swz = (uint32_t)((r >> 1) & 3);  // 64-byte TMA swizzle: chunk ^= (row / 2) % 4
         uint32_t it = 0;
         bool ok = true;
-        PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
             for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                 const int ps = it % SP, cs = it % S;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
-                PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertPacked);
@@ -420,7 +382,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(0)
                 const uint32_t src = pk0 + ps * Cfg::kPkStage + (uint32_t)r * kPkRowBytes;
                 uint4 w[H][4];
 #pragma unroll
@@ -429,7 +390,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     for (int c = 0; c < 4; ++c) w[h][c] = lds128(src + h * kPkSubA + (((uint32_t)c ^ swz) << 4));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));  // packed rows are in registers now
-                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -438,7 +398,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(2)
                 tc_fence_after_sync();
                 const uint32_t ta = tmem_a0 + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cs * Cfg::kAStageCols);
 #pragma unroll
@@ -457,21 +416,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(cv_full(cs), 0);
-                PROF(3)
             }
         }
-        if (warp == kFirstAConvWarp) { PROF_DUMP(3) }
     } else {
         // ------------------------------ B converters: packed smem -> swizzled int8 smem ------------------------------
         const int ctid = threadIdx.x - kFirstBConvWarp * 32;
         uint32_t it = 0;
         bool ok = true;
-        PROF_DECL
         for (int t = unit; t < num_tiles && ok; t += num_units) {
             for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
                 const int ps = it % SP, cs = it % S;
                 const uint32_t pph = (it / SP) & 1u, cph = (it / S) & 1u;
-                PROF(4)
                 if (!warp_wait<false>(pk_full(ps), pph, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertPacked);
@@ -480,7 +435,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(0)
                 const uint32_t src = pk0 + ps * Cfg::kPkStage + H * kPkSubA;
                 uint4 w[H][kBItersSub];
 #pragma unroll
@@ -489,7 +443,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     for (int j = 0; j < kBItersSub; ++j) w[h][j] = lds128(src + h * kPkSubB + (j * kBConvThreads + ctid) * 16);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pk_empty(ps));
-                PROF(1)
                 if (!warp_wait<false>(cv_empty(cs), cph ^ 1u, abort_flag, lane)) {
                     if (lane == 0) {
                         report_timeout(status, kWaitConvertSlot);
@@ -498,7 +451,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     ok = false;
                     break;
                 }
-                PROF(2)
                 tc_fence_after_sync();
                 const uint32_t dst = cv0 + cs * Cfg::kCvStage;
 #pragma unroll
@@ -511,10 +463,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(cv_full(cs), 0);
-                PROF(3)
             }
         }
-        if (warp == kFirstBConvWarp) { PROF_DUMP(4) }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -575,14 +525,16 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // static tile list: every pair of the grid must be resident at once
-    static int max_pairs[64] = {0};
-    int &cached = max_pairs[ctx.device & 63];
+    // per-device cache; the value is the same whichever thread computes it, so an atomic word is enough
+    static std::atomic<int> max_pairs[64];
+    int cached = max_pairs[ctx.device & 63].load(std::memory_order_relaxed);
     if (cached == 0) {
         cfg.gridDim = dim3((unsigned)(2 * (ctx.num_sms / 2)), 1, 1);
         int n = 0;
         cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
         if (qe != cudaSuccess) return record_cuda_error(qe, "cudaOccupancyMaxActiveClusters");
         cached = n > 0 ? n : 1;
+        max_pairs[ctx.device & 63].store(cached, std::memory_order_relaxed);
     }
     int units = ctx.num_sms / 2;
     if (cached < units) units = cached;
@@ -631,13 +583,5 @@ int tc2_launch_dequant(const GemmArgs &g, const DeviceCtx &ctx)
 {
     return tc2_launch_variant<2, true, true>(g, ctx, 1);
 }
-
-#ifdef QM_TC2_PROFILE
-extern "C" int qm_debug_tc2_profile(long long *out64)
-{
-    cudaError_t e = cudaMemcpyFromSymbol(out64, g_tc2_prof, sizeof(long long) * 128);
-    return e == cudaSuccess ? 0 : 4;
-}
-#endif
 
 }  // namespace qm

@@ -14,6 +14,7 @@
 //
 // The accumulators hold 256 x the true sums (K < 131072 keeps them inside int32, as on the tensor path).  Launches
 // chain through programmatic dependent launch like the decode kernel's.
+#include <atomic>
 #include <cstdlib>
 
 #include "qm_epilogue.cuh"
@@ -128,11 +129,11 @@ template <int MR, int RU>
 int launch_gemv(const GemmArgs &g, const DeviceCtx &ctx)
 {
     const size_t smem = (size_t)MR * (size_t)g.k;  // MR rows x k int8
-    static bool configured[64] = {false};
-    if (!configured[ctx.device & 63]) {
+    static std::atomic<bool> configured[64];  // set once per device; a repeated cudaFuncSetAttribute is harmless
+    if (!configured[ctx.device & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvMaxSmemBytes);
         if (e != cudaSuccess) return record_cuda_error(e, "cudaFuncSetAttribute(gemv shared memory)");
-        configured[ctx.device & 63] = true;
+        configured[ctx.device & 63].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     // enough warps that every SM has ~16 rows of B in flight; never more warps than row pairs

@@ -132,6 +132,10 @@ int unpack_launch(const uint8_t *in, int8_t *out, int64_t rows, int64_t k, cudaS
 int fill_launch(uint8_t *out, int64_t rows, int64_t k, uint64_t seed, cudaStream_t s);
 int unshard_launch(const int32_t *slabs, int32_t *C, int m, int n, int world, int64_t slab_stride, cudaStream_t s);
 
+// qm_peer_flags.cu: completion flags between GPUs (fused gather)
+int flag_signal_launch(int *flag, int value, cudaStream_t s);
+int flags_wait_launch(const int *flags, int count, int value, int timeout_ms, int *status, cudaStream_t s);
+
 // qm_api.cu
 // Column split of n over `world` ranks: whole units of 128 columns where n allows, the last ranks
 // take the remainder units.

@@ -17,6 +17,7 @@
 // arrival counters, which must start at zero, are cleared on the stream before every launch, and
 // the partial tiles are fully rewritten before they are read.  Two calls that overlap on the GPU
 // (different streams, no ordering) race on the scratch and give wrong results; order them.
+#include <atomic>
 #include <mutex>
 
 #include "qm_internal.h"
@@ -32,7 +33,6 @@ static __device__ __align__(256) int g_counters[kStaticCounters];
 static __device__ __align__(256) int g_status[2];  // in-kernel wait status of launches made through this entry point
 
 struct StaticCtx {
-    bool ready = false;
     int32_t *scratch = nullptr;
     int *counters = nullptr;
     qm::DeviceCtx dev;
@@ -40,6 +40,7 @@ struct StaticCtx {
 
 constexpr int kMaxDevices = 64;
 StaticCtx g_static[kMaxDevices];
+std::atomic<bool> g_static_ready[kMaxDevices];  // release-stored after g_static[dev] is complete
 std::mutex g_static_mutex;
 
 // First call on a device: resolve the device addresses of the arrays for THAT device.
@@ -50,9 +51,9 @@ int setup_current_device(StaticCtx **out)
     if (e != cudaSuccess) return qm::record_cuda_error(e, "cudaGetDevice");
     if (dev < 0 || dev >= kMaxDevices) return QM_ERR_ARG;
     StaticCtx &s = g_static[dev];
-    if (!s.ready) {
+    if (!g_static_ready[dev].load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_static_mutex);
-        if (!s.ready) {
+        if (!g_static_ready[dev].load(std::memory_order_relaxed)) {
             int major = 0, sms = 0;
             if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
                 return qm::record_cuda_error(e, "cudaDeviceGetAttribute");
@@ -75,7 +76,7 @@ int setup_current_device(StaticCtx **out)
             s.dev.num_sms = sms;
             s.dev.status = static_cast<int *>(p_status);
             s.dev.ready = true;
-            s.ready = true;
+            g_static_ready[dev].store(true, std::memory_order_release);
         }
     }
     *out = &s;
@@ -111,4 +112,26 @@ extern "C" int qm_gemm_s4_static_scratch(const void *A, const void *B, void *C, 
     }
     return qm::tc_launch_with_scratch(g, p, s->dev, s->scratch, kStaticScratchInts * sizeof(int32_t), s->counters,
                                       kStaticCounters);
+}
+
+// The status word of this entry point's launches.  Reads the file-scope word through the address resolved at set-up; a
+// device on which the entry point was never used has nothing to report.
+extern "C" int qm_static_scratch_status(int *code, int *where, int clear)
+{
+    if (code) *code = 0;
+    if (where) *where = 0;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return qm::record_cuda_error(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return QM_ERR_ARG;
+    if (!g_static_ready[dev].load(std::memory_order_acquire)) return QM_OK;
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return qm::record_cuda_error(e, "cudaDeviceSynchronize");
+    int words[2] = {0, 0};
+    int *status = g_static[dev].dev.status;
+    if ((e = cudaMemcpy(words, status, sizeof(words), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return qm::record_cuda_error(e, "cudaMemcpy(status)");
+    if (code) *code = words[0];
+    if (where) *where = words[1];
+    if (clear && (e = cudaMemset(status, 0, sizeof(words))) != cudaSuccess) return qm::record_cuda_error(e, "cudaMemset(status)");
+    return QM_OK;
 }

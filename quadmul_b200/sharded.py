@@ -86,13 +86,17 @@ class NShardedGemm:
     # -- fused gather: the GEMM epilogue writes straight into the destination rank's C ------------
     def local_into(self, a, b_shard, m: int, k: int, c_sym: "SymmetricC", dst: int = 0):
         """Compute this rank's column slab and store it, from inside the GEMM kernel, into rank `dst`'s
-        full-width C (peer-mapped memory, ordinary stores over NVLink; no staging, no NCCL).  Call
-        `c_sym.barrier()` afterwards: it returns once every rank's kernel has finished writing."""
+        full-width C (peer-mapped memory, ordinary stores over NVLink; no staging, no NCCL), then raise
+        this rank's completion flag on `dst` (stream-ordered after the GEMM).  A collective step: every
+        rank calls it once per product.  Rank `dst` calls `c_sym.wait_all()` afterwards: its stream
+        continues once every rank's slab has landed, or records a time-out (qm_device_status)."""
         target = c_sym.on_rank(dst)
         if tuple(target.shape) != (m, self.n):
             raise ValueError("SymmetricC shape does not match (m, n)")
-        return self.local(a, b_shard, m, k, out=target[:, self.begin : self.begin + self.count],
-                          plain_stores=(dst != self.rank))
+        out = self.local(a, b_shard, m, k, out=target[:, self.begin : self.begin + self.count],
+                         plain_stores=(dst != self.rank))
+        c_sym.signal(dst, self.rank)
+        return out
 
     # -- optional collective -------------------------------------------------------------
     def gather(self, slab, m: int, out=None):
@@ -142,12 +146,42 @@ class SymmetricC:
             device = torch.device("cuda", torch.cuda.current_device())
         self.local = symm.empty((self.m, self.n), dtype=torch.int32, device=device)
         self.handle = symm.rendezvous(self.local, self.group)
+        # one completion word per rank, in every rank's memory; `step` counts the products stored into this buffer
+        self.world = dist.get_world_size(self.group)
+        self.flags = symm.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flags_handle = symm.rendezvous(self.flags, self.group)
+        self.step = 0
+        torch.cuda.synchronize(device)
+        self.flags_handle.barrier()  # set-up only: every rank's flags are zero before anyone signals
 
     def on_rank(self, r: int):
         import torch
 
         return self.handle.get_buffer(int(r), (self.m, self.n), torch.int32)
 
+    def signal(self, dst: int, rank: int):
+        """Stream-ordered: this rank's earlier kernels are complete, system-wide, before word `rank` of rank `dst`'s flags
+        takes the new step number (qm_flag_signal).  Advances the step; every rank calls it once per product."""
+        import torch
+
+        from ._lib import LIB, check
+
+        self.step += 1
+        peer = self.flags_handle.get_buffer(int(dst), (64,), torch.int32)
+        check(LIB.qm_flag_signal(peer.data_ptr() + 4 * int(rank), self.step, torch.cuda.current_stream().cuda_stream), "flag_signal")
+
+    def wait_all(self, timeout_ms: int = 5000):
+        """On the destination rank: a kernel on the current stream that waits, for at most `timeout_ms`, until every rank
+        has signalled the current step (qm_flags_wait).  A time-out is reported by qm_device_status, not by a hang."""
+        import torch
+
+        from ._lib import LIB, check
+
+        check(LIB.qm_flags_wait(self.flags.data_ptr(), self.world, self.step, int(timeout_ms),
+                                torch.cuda.current_stream().cuda_stream), "flags_wait")
+
     def barrier(self):
-        """All ranks' earlier work on the current streams is complete when this returns on the stream."""
+        """Set-up and tests only (torch's symmetric-memory barrier): all ranks' earlier work on the current streams is
+        complete when this returns on the stream.  The data path uses signal / wait_all."""
         self.handle.barrier()

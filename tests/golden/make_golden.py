@@ -67,10 +67,13 @@ def cases():
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     import torch
 
     from oracle import oracle as o
+
+    ref_dir = sys.argv[1] if len(sys.argv) > 1 else o.reference_dir()
+    if ref_dir is None:
+        raise SystemExit("make_golden.py: pass the reference's directory (or set QUADMUL_REFERENCE_DIR)")
 
     assert o.build_ref(ref_dir), "reference build missing"
     assert o.ref_lib() is not None

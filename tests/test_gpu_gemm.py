@@ -408,6 +408,68 @@ def test_two_streams_run_large_gemms_concurrently(qm, cuda_clean, oracle):
         assert np.array_equal(c.cpu().numpy(), want)
 
 
+def test_two_streams_run_decode_shapes_concurrently(qm, cuda_clean, oracle):
+    """Decode shapes cut K and reduce through per-device scratch; every stream has a scratch slice of its own, so two
+    streams (and a third that reuses the first one's shapes) may overlap on the GPU.  Same call as the reference's, which
+    is stateless (kernel.cu:268-289)."""
+    torch = cuda_clean
+    shapes = [(16, 4096, 16384), (16, 11008, 8448), (16, 57344, 2048), (64, 1280, 16384)]
+    for m, n, k in shapes:
+        plan = qm.plan(m, n, k)
+        assert plan["kernel"] == 1 and plan["swap_ab"] == 2, plan  # the decode kernel with a K cut
+    ops = []
+    for i, (m, n, k) in enumerate(shapes):
+        ap = oracle.fill_packed(m, k, 190 + i); bp = oracle.fill_packed(n, k, 195 + i)
+        ops.append((m, n, k, to_dev(torch, ap), to_dev(torch, bp), torch.zeros((m, n), dtype=torch.int32, device="cuda"), oracle.gemm(ap, bp)))
+    streams = [torch.cuda.Stream() for _ in ops]
+    torch.cuda.synchronize()
+    for rep in range(25):
+        for (m, n, k, a, b, c, _), s in zip(ops, streams):
+            with torch.cuda.stream(s):
+                qm.gemm(a, b, c, m, n, k)
+    torch.cuda.synchronize()
+    for s in streams:
+        qm.release_stream(s)
+    for m, n, k, a, b, c, want in ops:
+        assert np.array_equal(c.cpu().numpy(), want), (m, n, k)
+
+
+def test_more_streams_than_scratch_slices_stay_correct(qm, cuda_clean, oracle):
+    """A stream that finds every scratch slice taken runs a form without scratch: same result."""
+    torch = cuda_clean
+    m, n, k = 16, 4096, 8192
+    ap = oracle.fill_packed(m, k, 291); bp = oracle.fill_packed(n, k, 292)
+    a, b, want = to_dev(torch, ap), to_dev(torch, bp), oracle.gemm(ap, bp)
+    streams = [torch.cuda.Stream() for _ in range(12)]
+    outs = [torch.zeros((m, n), dtype=torch.int32, device="cuda") for _ in streams]
+    torch.cuda.synchronize()
+    for s, c in zip(streams, outs):
+        with torch.cuda.stream(s):
+            qm.gemm_ex(a, b, c, m, n, k, kernel=1)  # the tensor path's table choice (a K cut through scratch)
+    torch.cuda.synchronize()
+    for s in streams:
+        qm.release_stream(s)
+    for c in outs:
+        assert np.array_equal(c.cpu().numpy(), want)
+
+
+def test_status_clear_also_resets_stale_arrival_counters(qm, cuda_clean, oracle):
+    """After a launch gave up on a wait its K partitions leave arrival counters non-zero.  qm_selftest_stale_counters puts
+    the scratch into that state from the host (a memset, nothing waits); qm_device_status(clear) must bring it back, and
+    the next split-K launches must then be exact."""
+    torch = cuda_clean
+    m, n, k = 16, 1024, 4096
+    ap = oracle.fill_packed(m, k, 391); bp = oracle.fill_packed(n, k, 392)
+    want = oracle.gemm(ap, bp)
+    split = dict(kernel=1, tile_n=16, swap_ab=2, cta_pair=1, split_k=4)
+    assert np.array_equal(run_gemm(qm, torch, ap, bp, **split), want)
+    qm.selftest_stale_counters()
+    assert qm.device_status(clear=True) == (0, 0)  # nothing timed out; the clear zeroes the counters as well
+    for opts in (split, dict(split, a_tmem=2), dict(split, a_tmem=2, split_k=0, stream_k=2)):
+        for _ in range(2):
+            assert np.array_equal(run_gemm(qm, torch, ap, bp, **opts), want), opts
+
+
 # ------------------------------------------------------------------ full-size configs
 def _where_differs(torch, got, want):
     """Which 32 x 32 blocks of two equal-shaped matrices differ (for the assertion message)."""
