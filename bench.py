@@ -377,7 +377,8 @@ def multi_gpu_legs(torch, dist, qm, world: int, rank: int, steps: int = 2) -> di
     a = qm.fill_packed(m, k, 4001)
     b_full = qm.fill_packed(n, k, 4002)
     b = sh.shard_of(b_full).contiguous()
-    seams = sorted({x for r in range(world) for x in (sh.ranges[r][0] - 1, sh.ranges[r][0], sh.ranges[r][0] + sh.ranges[r][1] - 1)})
+    seams = sorted({x for r in range(world) for x in (sh.ranges[r][0] - 1, sh.ranges[r][0], sh.ranges[r][0] + sh.ranges[r][1] - 1)
+                    if 0 <= x < n})
     slab = sh.local(a, b, m, k)
     full = sh.gather(slab, m)
     csym = SymmetricC(m, n)

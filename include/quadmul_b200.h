@@ -246,6 +246,21 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
                             int k, int64_t ldc, void *workspace, size_t workspace_bytes, void *stream);
 size_t qm_gemm_s4_dequant_workspace_bytes(int m, int n, int k, int64_t ldc, const void *out_bf16);
 
+/*
+ * Offline weight pre-layout for decode (optional; the plain layout stays the default everywhere).  Weights are static in
+ * inference, so B can be rearranged once: qm_prelayout_b writes B' (qm_prelayout_b_bytes(n, k) bytes: rows padded to 32,
+ * K to 4096 elements, still 4 bits per element) in the order in which the lanes of the register-resident decode kernel
+ * load it: every load instruction of a warp reads 512 consecutive bytes, a warp's 4 KB and a CTA's 64 KB per round are
+ * consecutive addresses.  qm_gemm_s4_prelaid is the product on such a B': same A, C and result as qm_gemm_s4,
+ * within that kernel's limits (m <= 16 with k <= 8192, or m <= 64 with k <= 4096; QM_ERR_ARG beyond: larger shapes take
+ * qm_gemm_s4 with the plain B), k % 32 == 0, 16-byte-aligned A and B'.
+ * The reference left the hook for this and never built it (reference kernel.cu:57 `#define PRESHUFFLE false`,
+ * kernel.cu:450 `reorganize_packed_B`).
+ */
+size_t qm_prelayout_b_bytes(int n, int k);
+int qm_prelayout_b(const void *B, void *B_pre, int n, int k, void *stream);
+int qm_gemm_s4_prelaid(const void *A, const void *B_pre, void *C, int m, int n, int k, void *stream);
+
 /* What the dispatcher would run for (m, n, k): fills *opts with the resolved choices. */
 int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts);
 

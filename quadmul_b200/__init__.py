@@ -174,6 +174,36 @@ def gemm_host(a, b, c, m: int, n: int, k: int) -> None:
     _launches += 1
 
 
+def prelayout_b(b, n: int, k: int):
+    """B (packed, n x k/2) -> the pre-laid-out form in which the register-resident decode kernel's loads are contiguous
+    (qm_prelayout_b).  Done once per weight matrix; returns a new 1-D int8 tensor."""
+    global _launches
+    torch = _torch()
+    if not b.is_cuda or b.element_size() != 1 or not b.is_contiguous() or b.numel() < n * (k // 2):
+        raise ValueError("prelayout_b: b must be a contiguous 1-byte CUDA tensor of n * k/2 bytes")
+    out = torch.empty(LIB.qm_prelayout_b_bytes(n, k), dtype=torch.int8, device=b.device)
+    with _on_device(b):
+        st = LIB.qm_prelayout_b(b.data_ptr(), out.data_ptr(), n, k, _stream_of(b))
+    check(st, f"prelayout_b(n={n}, k={k})")
+    _launches += 1
+    return out
+
+
+def gemm_prelaid(a, b_pre, c, m: int, n: int, k: int) -> None:
+    """C = A @ B^T with B given in the pre-laid-out form of prelayout_b (qm_gemm_s4_prelaid); m <= 16 with k <= 8192 or
+    m <= 64 with k <= 4096."""
+    global _launches
+    torch = _torch()
+    if not (a.is_cuda and b_pre.is_cuda and c.is_cuda) or c.dtype != torch.int32 or not (a.is_contiguous() and c.is_contiguous()):
+        raise ValueError("gemm_prelaid: CUDA tensors, contiguous a and c, int32 c")
+    if a.numel() < m * (k // 2) or c.numel() < m * n or b_pre.numel() < LIB.qm_prelayout_b_bytes(n, k):
+        raise ValueError("gemm_prelaid: tensor smaller than m, n, k imply")
+    with _on_device(a):
+        st = LIB.qm_gemm_s4_prelaid(a.data_ptr(), b_pre.data_ptr(), c.data_ptr(), m, n, k, _stream_of(a))
+    check(st, f"gemm_prelaid(m={m}, n={n}, k={k})")
+    _launches += 1
+
+
 def pack(x):
     """int8 tensor [rows, k] with values in [-8, 7] -> packed [rows, k/2] (dtype int8, like the
     reference's pack_b, test.py:6-15)."""

@@ -57,6 +57,9 @@ SIGNATURES = {
     "qm_static_scratch_status": (_i, [ctypes.POINTER(_i), ctypes.POINTER(_i), _i]),
     "qm_selftest_stale_counters": (_i, [_vp]),
     "qm_stream_release": (_i, [_vp]),
+    "qm_prelayout_b_bytes": (ctypes.c_size_t, [_i, _i]),
+    "qm_prelayout_b": (_i, [_vp, _vp, _i, _i, _vp]),
+    "qm_gemm_s4_prelaid": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "qm_flag_signal": (_i, [_vp, _i, _vp]),
     "qm_flags_wait": (_i, [_vp, _i, _i, _i, _vp]),
 }

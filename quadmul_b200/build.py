@@ -54,6 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-o",
         LIB_PATH,
     ]
+    cmd += os.environ.get("QM_NVCC_FLAGS", "").split()  # e.g. -DNAME for a development build
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += sources()

@@ -499,6 +499,37 @@ int qm_unshard_c(const void *slabs, void *C, int m, int n, int world, int64_t sl
                           static_cast<cudaStream_t>(stream));
 }
 
+size_t qm_prelayout_b_bytes(int n, int k)
+{
+    if (n <= 0 || k <= 0) return 0;
+    return prelayout_bytes(n, k);
+}
+
+int qm_prelayout_b(const void *B, void *B_pre, int n, int k, void *stream)
+{
+    if (n < 0 || k < 0 || (k % 32) != 0) return QM_ERR_SHAPE;
+    if (n == 0 || k == 0) return QM_OK;
+    if (!B || !B_pre) return QM_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(B) & 15u) || (reinterpret_cast<uintptr_t>(B_pre) & 15u)) return QM_ERR_ALIGN;
+    return prelayout_launch(static_cast<const uint8_t *>(B), static_cast<uint8_t *>(B_pre), n, k, static_cast<cudaStream_t>(stream));
+}
+
+int qm_gemm_s4_prelaid(const void *A, const void *B_pre, void *C, int m, int n, int k, void *stream)
+{
+    int st = check_gemm_args(A, B_pre, C, m, n, k, n);
+    if (st != QM_OK) return st;
+    if (m == 0 || n == 0) return QM_OK;
+    if (k == 0 || (k % 32) != 0) return QM_ERR_SHAPE;
+    DeviceCtx *ctx = nullptr;
+    st = ensure_ctx(&ctx);
+    if (st != QM_OK) return st;
+    GemmArgs g{static_cast<const uint8_t *>(A), static_cast<const uint8_t *>(B_pre), static_cast<int32_t *>(C), m, n, k, n,
+               static_cast<cudaStream_t>(stream)};
+    if (m > kRmmaMaxRows || k > (m <= 16 ? kRmmaMaxK : kRmmaMaxKTiled)) return QM_ERR_ARG;
+    if (!rmma_eligible(g)) return QM_ERR_ALIGN;
+    return rmma_launch_prelaid(g, *ctx);
+}
+
 int qm_flag_signal(int *flag, int value, void *stream)
 {
     if (!flag) return QM_ERR_NULL;

@@ -59,7 +59,10 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 
 __device__ __forceinline__ uint32_t word(const uint4 &v, int s) { return s == 0 ? v.x : (s == 1 ? v.y : (s == 2 ? v.z : v.w)); }
 
-template <int WARPS, int RG, int MS>
+// PRE: B is the pre-laid-out form written by prelayout_kernel below, [block of 8 RG rows][round][warp][step][row group][lane]
+// in 16-byte chunks: every load instruction of a warp reads 512 consecutive bytes, a warp's round is 4 KB and a CTA's round
+// 64 KB of consecutive addresses.
+template <int WARPS, int RG, int MS, bool PRE>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS == 16 ? 1 : 2))
 gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
                  uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
@@ -82,16 +85,28 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     const int g = lane >> 2, q = lane & 3;
     const int steps = (chunks + 3) / 4;  // chunk steps of a row: step t covers chunks 4t .. 4t+3
     const int num_blocks = (n + kRowsPerCta - 1) / kRowsPerCta;
+    const int rounds_k = (steps + kWarps * kMaxSteps - 1) / (kWarps * kMaxSteps);  // rounds of K a block takes (pre-laid-out form: padded)
+    // this lane's first chunk of (block rb, round r, this warp) in the pre-laid-out form; chunk (u, rg) is 32 * (u * RG + rg) further
+    auto pre_base = [&](int rb, int r) {
+        return reinterpret_cast<const uint4 *>(B) + (((int64_t)rb * rounds_k + r) * kWarps + warp) * (32 * kMaxSteps * kRowGroups) + lane;
+    };
 
     // L2 prefetch of one block of weights (this lane's share): returns no data, touches nothing the program can observe
     auto prefetch_block = [&](int rb) {
         if (rb >= num_blocks) return;
-        for (int t = warp; t < steps; t += kWarps) {
-            const int c = 4 * t + q;
+        if constexpr (PRE) {
+            // a warp's round is 32 * kMaxSteps * kRowGroups * 16 contiguous bytes: one 128-byte line per lane and 4 KB
+            for (int r = 0; r < rounds_k; ++r)
+                for (int b = 0; b < kMaxSteps * kRowGroups * 512; b += 4096)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(pre_base(rb, r) - lane) + b + lane * 128));
+        } else {
+            for (int t = warp; t < steps; t += kWarps) {
+                const int c = 4 * t + q;
 #pragma unroll
-            for (int rg = 0; rg < kRowGroups; ++rg) {
-                const int row = rb * kRowsPerCta + rg * 8 + g;
-                if (row < n && c < chunks) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
+                for (int rg = 0; rg < kRowGroups; ++rg) {
+                    const int row = rb * kRowsPerCta + rg * 8 + g;
+                    if (row < n && c < chunks) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
+                }
             }
         }
     };
@@ -111,15 +126,24 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     };
     // all loads of up to kMaxSteps chunk steps of block rb, starting at step t0
     auto load_round = [&](uint4(&w)[kMaxSteps][kRowGroups], int rb, int t0) {
+        if constexpr (PRE) {
+            // padded with zeros beyond n and k: no bounds to check
+            const uint4 *src = pre_base(rb, (t0 - warp) / (kWarps * kMaxSteps));
 #pragma unroll
-        for (int u = 0; u < kMaxSteps; ++u) {
-            const int t = t0 + u * kWarps;
-            const int c = 4 * t + q;
+            for (int u = 0; u < kMaxSteps; ++u)
 #pragma unroll
-            for (int rg = 0; rg < kRowGroups; ++rg) {
-                const int row = rb * kRowsPerCta + rg * 8 + g;
-                w[u][rg] = make_uint4(0, 0, 0, 0);
-                if (t < steps && c < chunks && row < n) w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                for (int rg = 0; rg < kRowGroups; ++rg) w[u][rg] = __ldcs(src + 32 * (u * kRowGroups + rg));
+        } else {
+#pragma unroll
+            for (int u = 0; u < kMaxSteps; ++u) {
+                const int t = t0 + u * kWarps;
+                const int c = 4 * t + q;
+#pragma unroll
+                for (int rg = 0; rg < kRowGroups; ++rg) {
+                    const int row = rb * kRowsPerCta + rg * 8 + g;
+                    w[u][rg] = make_uint4(0, 0, 0, 0);
+                    if (t < steps && c < chunks && row < n) w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                }
             }
         }
     };
@@ -227,11 +251,35 @@ bool rmma_eligible(const GemmArgs &g)
            (reinterpret_cast<uintptr_t>(g.B) & 15u) == 0;
 }
 
+// B (n x k/2 bytes) -> the pre-laid-out form of gemm_rmma_kernel<WARPS, RG, MS, true>; one thread per 16-byte chunk of B'.
 template <int WARPS, int RG, int MS>
+__global__ void __launch_bounds__(256) prelayout_kernel(const uint8_t *__restrict__ B, uint4 *__restrict__ Bp, int n, int k, int rounds_k,
+                                                        int64_t total_chunks)
+{
+    const int chunks = k / 32;
+    const int64_t row_bytes = k / 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_chunks; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t x = i;
+        const int lane = (int)(x % 32); x /= 32;
+        const int rg = (int)(x % RG); x /= RG;
+        const int u = (int)(x % MS); x /= MS;
+        const int w = (int)(x % WARPS); x /= WARPS;
+        const int r = (int)(x % rounds_k);
+        const int64_t rb = x / rounds_k;
+        const int g = lane >> 2, q = lane & 3;
+        const int64_t row = rb * (8 * RG) + rg * 8 + g;
+        const int c = 4 * (w + (r * MS + u) * WARPS) + q;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n && c < chunks) v = __ldg(reinterpret_cast<const uint4 *>(B + row * row_bytes) + c);
+        Bp[i] = v;
+    }
+}
+
+template <int WARPS, int RG, int MS, bool PRE>
 static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 {
     using Cfg = RmmaCfg<WARPS, RG, MS>;
-    auto kernel = gemm_rmma_kernel<WARPS, RG, MS>;
+    auto kernel = gemm_rmma_kernel<WARPS, RG, MS, PRE>;
     const int tiles = (g.m + 15) / 16;
     const size_t smem = (size_t)16 * tiles * (g.k / 2 + 64) + Cfg::kRedBytes;  // packed rows of A, padded by 64 bytes
     static std::atomic<bool> configured[64];  // set once per device; a repeated cudaFuncSetAttribute is harmless
@@ -267,7 +315,39 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
 {
     if (!rmma_eligible(g)) return QM_ERR_ARG;
-    return rmma_launch_cfg<16, 4, 2>(g, ctx);
+    return rmma_launch_cfg<16, 4, 2, false>(g, ctx);
+}
+
+// ---- offline weight pre-layout (optional) --------------------------------------------------------------------------
+// Weights are static in inference; the reference left a hook for rearranging them once and never built it (kernel.cu:57
+// `#define PRESHUFFLE false`, kernel.cu:450 `reorganize_packed_B`).  Here B' holds, for every 32-row block and every round of
+// 4096 K-elements, the chunks in the order the kernel's lanes load them.
+namespace {
+constexpr int kPreWarps = 16, kPreRG = 4, kPreMS = 2;  // the configuration the library runs
+int pre_rounds(int k) { return ((k / 32 + 3) / 4 + kPreWarps * kPreMS - 1) / (kPreWarps * kPreMS); }
+}  // namespace
+
+size_t prelayout_bytes(int n, int k)
+{
+    const size_t blocks = ((size_t)n + 8 * kPreRG - 1) / (8 * kPreRG);
+    return blocks * (size_t)pre_rounds(k) * kPreWarps * 32 * kPreMS * kPreRG * 16;
+}
+
+int prelayout_launch(const uint8_t *B, uint8_t *Bp, int n, int k, cudaStream_t s)
+{
+    const int64_t total_chunks = (int64_t)(prelayout_bytes(n, k) / 16);
+    if (total_chunks == 0) return QM_OK;
+    const int64_t blocks = (total_chunks + 255) / 256;
+    prelayout_kernel<kPreWarps, kPreRG, kPreMS><<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(
+        B, reinterpret_cast<uint4 *>(Bp), n, k, pre_rounds(k), total_chunks);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? QM_OK : record_cuda_error(e, "prelayout_kernel launch");
+}
+
+int rmma_launch_prelaid(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    if (!rmma_eligible(g)) return QM_ERR_ARG;
+    return rmma_launch_cfg<kPreWarps, kPreRG, kPreMS, true>(g, ctx);
 }
 
 }  // namespace qm

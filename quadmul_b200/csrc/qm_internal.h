@@ -120,6 +120,11 @@ inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
     if (m <= 32) return k <= kRmmaMaxKTiled && blocks <= 2 * num_sms;
     return m <= kRmmaMaxRows && k <= kRmmaMaxKTiled && blocks <= num_sms;
 }
+// offline weight layout for this kernel (optional): every warp-wide load reads 512 consecutive bytes, a warp's 4 KB and a
+// CTA's 64 KB per round contiguous; rows padded to 32, K to 4096 elements
+size_t prelayout_bytes(int n, int k);
+int prelayout_launch(const uint8_t *B, uint8_t *Bp, int n, int k, cudaStream_t s);
+int rmma_launch_prelaid(const GemmArgs &g, const DeviceCtx &ctx);  // g.B = the pre-laid-out form
 bool rmma_eligible(const GemmArgs &g);  // limits of the kernel itself (m <= 16, k <= kRmmaMaxK, any n) and 16-byte-aligned A and B
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx);
 

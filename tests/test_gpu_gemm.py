@@ -191,6 +191,32 @@ def test_register_resident_mma_kernel(qm, cuda_clean, oracle, m):
 
 
 # ------------------------------------------------------------------ seeded random shapes
+@pytest.mark.parametrize("m", [1, 7, 16, 23, 64])
+def test_prelaid_weights_give_the_same_product(qm, cuda_clean, oracle, m):
+    """qm_prelayout_b + qm_gemm_s4_prelaid: B rearranged once into the load order of the register-resident decode kernel (the
+    reference's unbuilt PRESHUFFLE hook, kernel.cu:57,450); gemm(A, prelayout(B)) must equal the oracle's A x B^T on the
+    plain B.  Ragged n (rows padded to 32), K below and between multiples of the 4096-element round, several blocks per
+    CTA; each twice in a row."""
+    torch = cuda_clean
+    cases = [(4096, 4096), (1000, 1024), (130, 256), (11008, 4096), (24, 800), (5000, 2336), (40000, 512), (17, 32)]
+    if m <= 16:
+        cases += [(4096, 8192), (300, 6144)]
+    for n, k in cases:
+        ap = oracle.fill_packed(m, k, 561); bp = oracle.fill_packed(n, k, 562)
+        want = oracle.gemm(ap, bp)
+        a, b = to_dev(torch, ap), to_dev(torch, bp)
+        b_pre = qm.prelayout_b(b, n, k)
+        assert b_pre.numel() == ((n + 31) // 32) * ((k + 4095) // 4096) * 65536
+        for _ in range(2):
+            c = torch.full((m, n), -9, dtype=torch.int32, device="cuda")
+            qm.gemm_prelaid(a, b_pre, c, m, n, k)
+            torch.cuda.synchronize()
+            assert np.array_equal(c.cpu().numpy(), want), (m, n, k)
+    with pytest.raises(qm.QuadmulError):  # beyond the kernel's limits: not this entry point's
+        a = qm.fill_packed(65, 256, 1); b_pre = qm.prelayout_b(qm.fill_packed(64, 256, 2), 64, 256)
+        qm.gemm_prelaid(a, b_pre, torch.zeros((65, 64), dtype=torch.int32, device="cuda"), 65, 64, 256)
+
+
 @pytest.mark.parametrize(
     "m,n,k",
     [

@@ -61,6 +61,51 @@ def test_call_on_a_device_that_is_not_current(qm, cuda_clean, oracle):
     assert code == 0
 
 
+def test_completion_flags_signal_then_wait(qm, cuda_clean):
+    """qm_flag_signal / qm_flags_wait on one device: flags that were signalled (stream order) satisfy the wait at once."""
+    torch = cuda_clean
+    from quadmul_b200 import _lib
+
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for step in (1, 2, 3):
+        for r in range(4):
+            assert _lib.LIB.qm_flag_signal(flags.data_ptr() + 4 * r, step, stream) == 0
+        assert _lib.LIB.qm_flags_wait(flags.data_ptr(), 4, step, 1000, stream) == 0
+    torch.cuda.synchronize()
+    assert flags[:4].tolist() == [3, 3, 3, 3]
+    assert _lib.LIB.qm_flags_wait(flags.data_ptr(), 4, 2, 1000, stream) == 0  # an older step is satisfied too
+    assert _lib.LIB.qm_flags_wait(None, 4, 1, 1000, stream) == 1
+    assert _lib.LIB.qm_flags_wait(flags.data_ptr(), 65, 1, 1000, stream) == 8
+    assert _lib.LIB.qm_flags_wait(flags.data_ptr(), 4, 1, 0, stream) == 8
+
+
+def test_completion_flag_that_nobody_raises_times_out(qm, oracle):
+    """The wait of the fused gather is bounded: with a flag that no rank ever raises the kernel gives up after its limit,
+    returns, and the status word reports QM_ERR_TIMEOUT at the peer-wait site; the context stays usable.  Nothing faults and
+    nothing spins without end: the flag simply never arrives."""
+    import time
+
+    import torch
+
+    from _util import run_gemm
+    from quadmul_b200 import _lib
+
+    qm.device_status(clear=True)
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert _lib.LIB.qm_flag_signal(flags.data_ptr(), 1, stream) == 0  # rank 0 arrives, rank 1 never does
+    t0 = time.time()
+    assert _lib.LIB.qm_flags_wait(flags.data_ptr(), 2, 1, 200, stream) == 0
+    code, where = qm.device_status(clear=True)  # synchronises
+    elapsed = time.time() - t0
+    assert code == 5 and (where & 0xFF) == 8 and (where >> 8) == 1, (code, where)  # QM_ERR_TIMEOUT, peer wait, flag 1
+    assert 0.15 < elapsed < 5.0, elapsed
+    ap = oracle.fill_packed(16, 256, 1); bp = oracle.fill_packed(300, 256, 2)
+    assert np.array_equal(run_gemm(qm, torch, ap, bp), oracle.gemm(ap, bp))
+    assert qm.device_status(clear=True) == (0, 0)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -97,10 +142,14 @@ def _nccl_worker(rank, world, port, m, n, k, q):
 
         csym = SymmetricC(m, n)
         csym.local.fill_(-3)
-        csym.barrier()
-        sh.local_into(a, b, m, k, csym, dst=0)
-        csym.barrier()
         torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(2):  # twice: the step number of the completion flags advances
+            sh.local_into(a, b, m, k, csym, dst=0)
+            if rank == 0:
+                csym.wait_all()  # completion flags in rank 0's memory, bounded wait
+        torch.cuda.synchronize()
+        dist.barrier()
         if rank == 0:
             ok = ok and bool(np.array_equal(csym.local.cpu().numpy(), want))
         else:
