@@ -315,6 +315,36 @@ EXTRA_SHAPES = [  # (m, n, k, kind): the decode and prefill shapes of the target
 ]
 
 
+def time_prelaid(torch, qm, m, n, k, per_graph, replays):
+    """The same product through qm_gemm_s4_prelaid: B rearranged once (untimed, as a weight loader would) into the load
+    order of the register-resident decode kernel."""
+    per_launch_bytes = m * k // 2 + n * k // 2 + 4 * m * n
+    rotate = min(64, int(2 * 126e6 // per_launch_bytes) + 2)
+    a = qm.fill_packed(m, k, 1002)
+    bs = [qm.fill_packed(n, k, 3002 + 17 * i) for i in range(rotate)]
+    bps = [qm.prelayout_b(b, n, k) for b in bs]
+    cs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(rotate)]
+    qm.gemm_prelaid(a, bps[0], cs[0], m, n, k)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(per_graph):
+            qm.gemm_prelaid(a, bps[i % rotate], cs[i % rotate], m, n, k)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / per_graph)
+    times.sort()
+    return times[0], times[len(times) // 2], (a, bs[0], cs[0]), rotate
+
+
 def extra_legs(torch, qm) -> list:
     """Further shapes, each verified against the oracle and then timed; not part of the headline number."""
     out = []
@@ -342,6 +372,16 @@ def extra_legs(torch, qm) -> list:
         out.append(e)
         del a, b, c
         torch.cuda.empty_cache()
+        if kind == "decode" and k <= 8192 and n * k <= 64 * 2**20:
+            # the optional offline weight layout (qm_prelayout_b): same product, same bytes, verified against the PLAIN B
+            t_min, t_med, (a, b, c), rotate = time_prelaid(torch, qm, m, n, k, per_graph, replays)
+            ver = verify_against_oracle(torch, a, b, c, m, n, k, points=1024, seed=m + n + k + 1)
+            gbs = nbytes / (t_med * 1e-3) / 1e9
+            out.append({"shape": [m, n, k], "kind": "decode, pre-laid-out weights (qm_gemm_s4_prelaid)", "us_min": t_min * 1e3,
+                        "us_median": t_med * 1e3, "verified": ver["ok"], "buffers_in_rotation": rotate, "cuda_graph_launches": per_graph,
+                        "bound": "hbm", "gbs": gbs, "frac": gbs / peak_h, "algorithmic_bytes": nbytes})
+            del a, b, c
+            torch.cuda.empty_cache()
     return out
 
 

@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libquadmul_b200.so")
 SOURCES = ["qm_api.cu", "qm_gemm_tc.cu", "qm_gemm_tc2.cu", "qm_gemm_dec.cu", "qm_gemv.cu", "qm_gemm_rmma.cu", "qm_gemm_simt.cu", "qm_pack.cu", "qm_dequant.cu", "qm_static_scratch.cu", "qm_peer_flags.cu"]
-HEADERS = ["qm_internal.h", "qm_ptx.cuh", "qm_tile_table.h", "qm_tc_common.cuh", "qm_epilogue.cuh", os.path.join("..", "..", "include", "quadmul_b200.h")]
+HEADERS = ["qm_internal.h", "qm_ptx.cuh", "qm_tile_table.h", "qm_tc_common.cuh", "qm_epilogue.cuh", "tile_table.inc", os.path.join("..", "..", "include", "quadmul_b200.h")]
 
 
 def nvcc_path() -> str:

@@ -163,9 +163,13 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
     const bool eligible = tc_eligible(g);
     if (kernel == QM_KERNEL_TC && !eligible) return QM_ERR_ALIGN;
     if (kernel == QM_KERNEL_GEMV && !gemv_eligible(g)) return m > kGemvMaxRows ? QM_ERR_ARG : QM_ERR_ALIGN;
-    // small decode shapes: the register-resident kernel, else (one to four rows) the dp4a row kernel; rules in qm_internal.h
-    if (kernel == QM_KERNEL_AUTO && rmma_eligible(g) && rmma_shape_ok(m, n, k, ctx->num_sms)) return rmma_launch(g, *ctx);
-    if (kernel == QM_KERNEL_AUTO && gemv_eligible(g) && gemv_shape_ok(m, n, k)) kernel = QM_KERNEL_GEMV;
+    // decode shapes: the generated table (swept shapes, else the cost model) picks among the families that can take the call
+    if (kernel == QM_KERNEL_AUTO && m <= kRmmaMaxRows) {
+        const bool ok[3] = {rmma_eligible(g), gemv_eligible(g), eligible};
+        const int fam = choose_decode_family(m, n, k, ctx->num_sms, ok);
+        if (fam == kFamRmma) return rmma_launch(g, *ctx);
+        if (fam == kFamGemv) kernel = QM_KERNEL_GEMV;
+    }
     if (kernel == QM_KERNEL_AUTO) kernel = eligible ? QM_KERNEL_TC : QM_KERNEL_SIMT;
     if (kernel == QM_KERNEL_SIMT) return simt_launch(g);
     if (kernel == QM_KERNEL_GEMV) return gemv_launch(g, *ctx);
@@ -337,8 +341,12 @@ int qm_gemm_s4_dequant_bf16(const void *A, const void *B, const float *scale_a, 
         g.out_bf16 = out_bf16, g.scale_a = scale_a, g.scale_b = scale_b;
         const TcPlan p = plan_tc(m, n, k, ctx->num_sms);
         // fused: the large-shape, the decode and the dp4a row kernel convert inside their epilogues and never write the int32 matrix
-        if (rmma_eligible(g) && rmma_shape_ok(m, n, k, ctx->num_sms)) return rmma_launch(g, *ctx);
-        if (gemv_eligible(g) && gemv_shape_ok(m, n, k)) return gemv_launch(g, *ctx);
+        if (m <= kRmmaMaxRows) {
+            const bool ok[3] = {rmma_eligible(g), gemv_eligible(g), tc_eligible(g)};
+            const int fam = choose_decode_family(m, n, k, ctx->num_sms, ok);
+            if (fam == kFamRmma) return rmma_launch(g, *ctx);
+            if (fam == kFamGemv) return gemv_launch(g, *ctx);
+        }
         if (tc_eligible(g) && p.a_tmem && !p.swap_ab && tc2_can_dequant(g)) return tc2_launch_dequant(g, *ctx);
         if (tc_eligible(g) && p.a_tmem && p.swap_ab) {
             TcPlan q = p;
@@ -603,9 +611,12 @@ int qm_plan(int m, int n, int k, qm_gemm_opts_t *opts)
         return QM_OK;
     }
     TcPlan p = plan_tc(m, n, k, 148);
-    opts->kernel = rmma_shape_ok(m, n, k, 148)        ? QM_KERNEL_RMMA
-                   : gemv_shape_ok(m, n, k)           ? QM_KERNEL_GEMV
-                                                      : QM_KERNEL_TC;
+    opts->kernel = QM_KERNEL_TC;
+    if (m >= 1 && m <= kRmmaMaxRows) {  // aligned operands assumed
+        const bool ok[3] = {rmma_shape_limits(m, k), gemv_shape_limits(m, k), true};
+        const int fam = choose_decode_family(m, n, k, 148, ok);
+        opts->kernel = fam == kFamRmma ? QM_KERNEL_RMMA : (fam == kFamGemv ? QM_KERNEL_GEMV : QM_KERNEL_TC);
+    }
     opts->tile_n = p.tile_n;
     opts->swap_ab = p.swap_ab + 1;
     opts->split_k = p.split_k;

@@ -89,14 +89,11 @@ int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
 // qm_gemv.cu: one to four rows of A, weight streaming with dp4a (no tensor cores); int32 or fused bf16 output
 constexpr int kGemvMaxRows = 4;
 constexpr size_t kGemvMaxSmemBytes = 200 * 1024;  // converted rows of A held by a CTA
-// Shapes the table gives to the row kernel: one or two rows of A always (HBM-bound at every size: 1 x 28672 x 8192 runs at
-// 4.9 TB/s); three or four rows while the problem is small enough to be latency-bound (4 x 4096 x 4096: 6.3 us against 8.0 us
-// on the tensor path), not beyond (4 x 11008 x 4096: 11.3 against 10.6 us; 4 x 28672 x 8192: 43 against 28 us, dp4a-bound).
-inline bool gemv_shape_ok(int m, int n, int k)
+// Shape limits of the row kernel (the table decides among the eligible kernel families in qm_tile_table.h).
+inline bool gemv_shape_limits(int m, int k)
 {
     if (m < 1 || m > kGemvMaxRows || k % 32 != 0 || k >= 131072) return false;
-    if ((size_t)(m <= 1 ? 1 : (m <= 2 ? 2 : 4)) * (size_t)k > kGemvMaxSmemBytes) return false;
-    return m <= 2 || (int64_t)n * k <= (int64_t)32 * 1024 * 1024;
+    return (size_t)(m <= 1 ? 1 : (m <= 2 ? 2 : 4)) * (size_t)k <= kGemvMaxSmemBytes;
 }
 bool gemv_eligible(const GemmArgs &g);  // shape limits of the kernel itself (any n) and 16-byte-aligned A and B
 int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx);
@@ -105,20 +102,10 @@ int gemv_launch(const GemmArgs &g, const DeviceCtx &ctx);
 constexpr int kRmmaMaxK = 8192;  // 16 converted rows of A (16 * K bytes) + 32 KB of partial tiles fit in shared memory
 constexpr int kRmmaMaxRows = 64;       // rows of A, in tiles of 16 that pass through shared memory one after the other
 constexpr int kRmmaMaxKTiled = 4096;   // ... which needs a block's weights resident in registers (16 warps x 2 steps x 128 elements)
-// Shapes the table gives it, from sweeps on B200 (us per launch, this kernel against the next best):
-//   up to 16 rows of A, K <= 8192: while the 32-row blocks of B fit the SMs in at most four rounds (16 x 4096 x 4096 3.9 / 8.2,
-//   16 x 11008 x 4096 9.1 / 10.5, 16 x 16384 x 4096 12.1, 16 x 8192 x 8192 11.5 / 12.4; beyond: 16 x 28672 x 4096 18.5 / 15.9);
-//   one or two rows: only one round (2 x 4096 x 4096 3.8 / 4.7 on the row kernel, which streams better beyond: 1 x 11008 x 4096 7.7);
-//   17-32 rows (K <= 4096): two rounds (32 x 4096 x 4096 5.9 / 9.4, 32 x 8192 x 4096 9.4 / 10.7, 32 x 11008 x 4096 12.8 / 12.2);
-//   33-64 rows (K <= 4096): one round (64 x 4096 x 4096 9.1 / 11.8, 64 x 8192 x 4096 14.5 / 12.9).
-inline bool rmma_shape_ok(int m, int n, int k, int num_sms)
+// Shape limits of the kernel (the table decides among the eligible kernel families in qm_tile_table.h).
+inline bool rmma_shape_limits(int m, int k)
 {
-    if (m < 1 || k % 32 != 0) return false;
-    const int blocks = (n + 31) / 32;
-    if (m <= 2) return k <= kRmmaMaxK && blocks <= num_sms;
-    if (m <= 16) return k <= kRmmaMaxK && blocks <= 4 * num_sms;
-    if (m <= 32) return k <= kRmmaMaxKTiled && blocks <= 2 * num_sms;
-    return m <= kRmmaMaxRows && k <= kRmmaMaxKTiled && blocks <= num_sms;
+    return m >= 1 && m <= kRmmaMaxRows && k % 32 == 0 && k <= (m <= 16 ? kRmmaMaxK : kRmmaMaxKTiled);
 }
 // offline weight layout for this kernel (optional): every warp-wide load reads 512 consecutive bytes, a warp's 4 KB and a
 // CTA's 64 KB per round contiguous; rows padded to 32, K to 4096 elements

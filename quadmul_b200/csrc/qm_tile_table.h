@@ -4,6 +4,7 @@
 // plan, chosen by the rules below.
 #pragma once
 #include "qm_internal.h"
+#include "tile_table.inc"  // generated: swept shapes and the cost-model coefficients of the decode kernel families
 
 namespace qm {
 
@@ -28,6 +29,57 @@ static const PlanRule kPlanRules[] = {
     {64, 1, 64, 1},
     {0x7FFFFFFF, 0, 256, 2},
 };
+
+// ---- decode shapes (m <= 64): which kernel family ----------------------------------------------------------------
+// Three families take a product with few rows of A: gemm_rmma_kernel, gemv_kernel, gemm_dec_kernel.  A shape that was swept
+// on B200 runs the family measured fastest there (exact-match entry of the generated table); any other shape runs the
+// family whose modelled time -- a linear form in a few structural features, fitted to the same sweep -- is smallest.
+// `quadmul_b200/tile_table_gen.py` holds the same feature expressions.
+enum DecodeFamily : int { kFamNone = -1, kFamRmma = 0, kFamGemv = 1, kFamDec = 2 };
+
+inline double decode_cost(int family, int m, int n, int k, int num_sms)
+{
+    const double mb = (double)n * k / 2 / 1e6;
+    if (family == kFamRmma) {
+        const double rounds = (double)(((n + 31) / 32 + num_sms - 1) / num_sms), tiles = (double)((m + 15) / 16), kq = k / 4096.0;
+        const double *c = table::kRmmaCost;
+        return c[0] + c[1] * rounds + c[2] * kq + c[3] * rounds * kq + c[4] * tiles + c[5] * rounds * tiles;
+    }
+    if (family == kFamGemv) {
+        const double *c = table::kGemvCost;
+        return c[0] + c[1] * mb + c[2] * m * mb + c[3] * m;
+    }
+    const double *c = table::kDecCost[m <= 16 ? 0 : (m <= 32 ? 1 : 2)];
+    return c[0] + c[1] * mb + c[2] * m + c[3] * m * mb;
+}
+
+// `ok[f]`: family f can take this call (shape limits and operand alignment).  Returns kFamNone when none can.
+inline int choose_decode_family(int m, int n, int k, int num_sms, const bool (&ok)[3])
+{
+    if (num_sms == table::kSweepSms) {
+        // swept shapes, sorted by (m, n, k): binary search
+        int lo = 0, hi = table::kNumSwept - 1;
+        while (lo <= hi) {
+            const int mid = (lo + hi) / 2;
+            const table::Swept &s = table::kSwept[mid];
+            const int cmp = s.m != m ? (s.m < m ? -1 : 1) : (s.n != n ? (s.n < n ? -1 : 1) : (s.k != k ? (s.k < k ? -1 : 1) : 0));
+            if (cmp == 0) {
+                if (ok[s.family]) return s.family;
+                break;
+            }
+            if (cmp < 0) lo = mid + 1;
+            else hi = mid - 1;
+        }
+    }
+    int best = kFamNone;
+    double best_t = 0;
+    for (int f = 0; f < 3; ++f) {
+        if (!ok[f]) continue;
+        const double t = decode_cost(f, m, n, k, num_sms);
+        if (best == kFamNone || t < best_t) best = f, best_t = t;
+    }
+    return best;
+}
 
 inline bool tc_eligible(const GemmArgs &g)
 {

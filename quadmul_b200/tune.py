@@ -78,15 +78,56 @@ def time_variant(qm, torch, m, n, k, opts, iters, per_graph):
     return best, code
 
 
+# Shapes of the kernel-family sweep behind the decode cost model: rows of A x (N, K) of common layer shapes.
+FAMILY_M = [1, 2, 4, 8, 16, 24, 32, 48, 64]
+FAMILY_NK = [(2048, 4096), (4096, 4096), (6144, 4096), (8192, 4096), (11008, 4096), (16384, 4096), (28672, 4096), (2048, 8192),
+             (4096, 8192), (8192, 8192), (10240, 8192), (28672, 8192), (57344, 8192), (4096, 2048), (4096, 11008), (4096, 14336)]
+FAMILIES = {"rmma": dict(kernel=4), "gemv": dict(kernel=3), "dec": dict(kernel=1)}  # dec: the tensor path with the table's K cut
+
+
+def family_sweep(qm, torch, iters, out):
+    """One line per (shape, kernel family): the register-resident kernel, the row kernel and the TMA/TMEM decode kernel, each
+    in the form the table would run it.  These lines are what `--emit` fits the cost model to."""
+    for n, k in FAMILY_NK:
+        for m in FAMILY_M:
+            for fam, opts in FAMILIES.items():
+                try:
+                    ms, code = time_variant(qm, torch, m, n, k, opts, iters, 50 if n * k < 64e6 else 20)
+                except qm.QuadmulError as exc:
+                    if exc.status in (3, 7, 8):  # this family does not take the shape
+                        continue
+                    raise
+                if code != 0:
+                    raise SystemExit(f"tune: in-kernel wait expired for {m}x{n}x{k} {fam}; stopping")
+                line = json.dumps({"family": fam, "m": m, "n": n, "k": k, "us": round(ms * 1e3, 2)})
+                print(line, flush=True)
+                if out:
+                    out.write(line + "\n")
+                    out.flush()
+
+
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default=None)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--families", action="store_true", help="sweep the decode kernel families (input of --emit)")
+    ap.add_argument("--out", default=None, help="with --families: also append the lines to this file")
+    ap.add_argument("--emit", action="store_true", help="no GPU: fit the cost model to the committed sweep and write csrc/tile_table.inc")
+    ap.add_argument("--check", action="store_true", help="with --emit: do not write, exit 1 if csrc/tile_table.inc would change")
+    args = ap.parse_args()
+    if args.emit:
+        from . import tile_table_gen
+
+        raise SystemExit(tile_table_gen.main(check=args.check))
     import torch
 
     import quadmul_b200 as qm
 
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--shapes", default=None)
-    ap.add_argument("--iters", type=int, default=10)
-    args = ap.parse_args()
+    if args.families:
+        qm.init()
+        with (open(args.out, "a") if args.out else open("/dev/null", "w")) as out:
+            family_sweep(qm, torch, args.iters, out if args.out else None)
+        return
     shapes = DEFAULT_SHAPES if not args.shapes else [tuple(int(x) for x in s.split(",")) for s in args.shapes.split(";")]
     qm.init()
     for m, n, k in shapes:

@@ -105,12 +105,13 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
         for n in (1, 8, 100, 128, 129, 1000, 4096, 11008, 57344):
             for k in (32, 128, 512, 4096, 28672):
                 p = qm.plan(m, n, k)
-                blocks = (n + 31) // 32  # register-resident kernel: rounds of 32-row blocks of B over 148 SMs
-                rmma = ((m <= 2 and k <= 8192 and blocks <= 148) or (3 <= m <= 16 and k <= 8192 and blocks <= 592)
-                        or (17 <= m <= 32 and k <= 4096 and blocks <= 296) or (33 <= m <= 64 and k <= 4096 and blocks <= 148))
-                gemv = m <= 2 or (m <= 4 and n * k <= 32 * 2**20)  # one to four rows: dp4a row kernel
-                want = _lib.QM_KERNEL_RMMA if rmma else _lib.QM_KERNEL_GEMV if gemv else _lib.QM_KERNEL_TC
-                assert p["kernel"] == want
+                # decode shapes: the generated table picks among the families whose limits admit the shape
+                allowed = {_lib.QM_KERNEL_TC}
+                if m <= 64 and k <= (8192 if m <= 16 else 4096):
+                    allowed.add(_lib.QM_KERNEL_RMMA)  # register-resident kernel
+                if m <= 4:
+                    allowed.add(_lib.QM_KERNEL_GEMV)  # dp4a row kernel
+                assert p["kernel"] in allowed, (m, n, k, p)
                 assert p["tile_n"] in (16, 32, 64, 128, 256)
                 swap, pair, tm = p["swap_ab"] == 2, p["cta_pair"] == 2, p["a_tmem"] == 2
                 blocks = (k + 255) // 256 if tm else (k + 127) // 128
@@ -144,3 +145,25 @@ def test_drop_in_module_name():
     import quadmul
 
     assert callable(quadmul.gemm) and callable(quadmul.pack_b)
+
+
+def test_generated_tile_table_matches_the_committed_sweep():
+    """csrc/tile_table.inc is generated (`python -m quadmul_b200.tune --emit`) from the committed B200 sweep
+    quadmul_b200/tune_sweep_b200.jsonl: regenerating it must reproduce the committed file byte for byte."""
+    from quadmul_b200 import tile_table_gen as gen
+
+    assert open(gen.INC_PATH).read() == gen.render(gen.load_sweep())
+
+
+def test_plan_follows_the_sweep_and_the_cost_model(qm):
+    """Every swept decode shape resolves to the kernel family that was fastest in the sweep; a shape between swept points
+    resolves to one of the families, never to nothing (the reference does nothing for an unknown shape, kernel.cu:340-385)."""
+    from quadmul_b200 import tile_table_gen as gen
+
+    kernel_of_family = {0: 4, 1: 3, 2: 1}  # QM_KERNEL_RMMA, QM_KERNEL_GEMV, QM_KERNEL_TC
+    for m, n, k, fam, _ in gen.best_per_shape(gen.load_sweep()):
+        assert qm.plan(m, n, k)["kernel"] == kernel_of_family[fam], (m, n, k)
+    for m, n, k in [(3, 5000, 4096), (12, 7168, 4096), (20, 12288, 4096), (40, 3072, 8192), (16, 100000, 4096), (1, 512, 2048), (64, 64, 64)]:
+        assert qm.plan(m, n, k)["kernel"] in (1, 3, 4)
+    assert qm.plan(16, 4096, 16384)["kernel"] == 1   # K beyond the register-resident kernel's limit
+    assert qm.plan(16, 200000, 4096)["kernel"] == 1  # far beyond the sweep: the streaming kernel's slope wins

