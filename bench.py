@@ -47,8 +47,8 @@ UNIT = "TOPS"
 INT8_PEAK_NOMINAL_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
 FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the headline kernel at 8192^3, from an ncu capture of this
-# command (`--steps 2 --warmup 3 --no-cpu-baseline --no-e2e --no-extra`, one launch captured): 164.6 MB read + 222.1 MB written
-DRAM_TRAFFIC_BYTES_PER_LAUNCH = 386.7e6
+# command (`--steps 2 --warmup 3 --no-cpu-baseline --no-e2e --no-extra`, one launch captured): 164.3 MB read + 220.5 MB written
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = 384.7e6
 
 
 def config(n_gpus: int) -> dict:
@@ -583,10 +583,19 @@ def native_arm(args) -> None:
               [torch.empty((m, n_local), dtype=torch.bfloat16, device="cuda") for _ in range(rotate)])
         per_launch_bytes = m * k // 2 + b_bytes + 2 * m * n_local + 4 * (m + n_local)
 
+    bps = None
+    if args.prelaid:
+        # the optional offline weight layout: B rearranged once, outside every timed region, as a weight loader would
+        if world != 1 or forced or large or dq is not None:
+            raise SystemExit("bench.py: --prelaid is a single-GPU option without forced tiles")
+        bps = [qm.prelayout_b(b_i, n_local, k) for b_i in bs]
+
     def launch():
         i = counter[0] % rotate
         counter[0] += 1
-        if dq is not None:
+        if bps is not None:
+            qm.gemm_prelaid(a, bps[i], cs[i], m, n_local, k)
+        elif dq is not None:
             qm.gemm_dequant(a, bs[i], dq[0], dq[1], dq[2][i], m, n_local, k, workspace=cs[i].view(-1))
         elif forced:
             qm.gemm_ex(a, bs[i], cs[i], m, n_local, k, kernel=1, **forced)
@@ -668,7 +677,8 @@ def native_arm(args) -> None:
             achieved = per_launch_bytes / (avg_launch_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak}
         roofline.update({
-            "kernel": ("gemv_kernel<dp4a, weight streaming>" if plan.get("kernel") == 3 and not forced else
+            "kernel": ("gemm_rmma_kernel<pre-laid-out weights into registers, mma.sync s8>" if bps is not None else
+                       "gemv_kernel<dp4a, weight streaming>" if plan.get("kernel") == 3 and not forced else
                        "gemm_rmma_kernel<weights into registers, mma.sync s8>" if plan.get("kernel") == 4 and not forced else
                        f"gemm_dec_kernel<tile_n={plan['tile_n']}, B rows through TMEM, " +
                        ("balanced shares" if plan.get("stream_k") == 2 else f"split_k={plan['split_k']}") + ">"
@@ -760,7 +770,7 @@ def native_arm(args) -> None:
             }
             line["gpu_launches"] += e2e_steps + 1
 
-    headline = not custom and not large and not forced and dq is None and args.graph == 0
+    headline = not custom and not large and not forced and dq is None and args.graph == 0 and bps is None
     if headline and not args.no_extra:
         del bs, cs, c, a
         torch.cuda.empty_cache()
@@ -849,6 +859,8 @@ def main() -> None:
     ap.add_argument("--l2-resident", action="store_true",
                     help="with --shape: reuse one B and C buffer so that a small problem is served from L2 (the latency floor of "
                          "the launch; never the roofline number)")
+    ap.add_argument("--prelaid", action="store_true",
+                    help="with --shape (a decode shape): time qm_gemm_s4_prelaid on weights rearranged once by qm_prelayout_b")
     ap.add_argument("--dequant", action="store_true",
                     help="time qm_gemm_s4_dequant_bf16 (bf16 output with row and column scales) instead of the int32 GEMM")
     ap.add_argument("--op", choices=["gemm", "pack", "unpack"], default="gemm",

@@ -28,12 +28,13 @@ std::atomic<uintptr_t> g_slice_key[kMaxDevices][kNumSlices];  // which stream ow
 std::mutex g_mutex;
 thread_local std::string t_last_error;
 
-constexpr int kHostSlabs = 8;  // row slabs whose result copy overlaps the next slab's upload and GEMM
+constexpr int kHostSlabs = 8;   // row slabs whose result copy overlaps the next slab's upload and GEMM
+constexpr int kHostBParts = 4;  // blocks of B rows the first slab takes one by one, so that the first download starts early
 struct HostStage {             // grow-only device buffers, copy stream and events of qm_gemm_s4_host
     void *a = nullptr, *b = nullptr, *c = nullptr;
     size_t a_bytes = 0, b_bytes = 0, c_bytes = 0;
     cudaStream_t copy_stream = nullptr;
-    cudaEvent_t slab_done[kHostSlabs] = {};
+    cudaEvent_t slab_done[kHostSlabs + kHostBParts] = {};
     bool streams_ready = false;
 };
 HostStage g_stage[kMaxDevices];
@@ -420,21 +421,26 @@ int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int 
     if ((e = grow(s.b, s.b_bytes, b_bytes ? b_bytes : 16)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(B)");
     if ((e = grow(s.c, s.c_bytes, c_bytes)) != cudaSuccess) return record_cuda_error(e, "cudaMalloc(C)");
     cudaStream_t stream = cudaStreamPerThread;
-    if (b_bytes && (e = cudaMemcpyAsync(s.b, hB, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
-        return record_cuda_error(e, "cudaMemcpyAsync(B)");
     // Large results: cut C into row slabs and copy slab i back on a second stream while slab i+1 is uploaded and
     // computed, so the two PCIe directions and the GEMM overlap.  Small ones: one upload, one GEMM, one download.
     const int slabs = (c_bytes >= (32u << 20) && m >= 256 * kHostSlabs) ? kHostSlabs : 1;
     if (slabs > 1 && !s.streams_ready) {
         if ((e = cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking)) != cudaSuccess)
             return record_cuda_error(e, "cudaStreamCreate");
-        for (int i = 0; i < kHostSlabs; ++i)
+        for (int i = 0; i < kHostSlabs + kHostBParts; ++i)
             if ((e = cudaEventCreateWithFlags(&s.slab_done[i], cudaEventDisableTiming)) != cudaSuccess)
                 return record_cuda_error(e, "cudaEventCreate");
         s.streams_ready = true;
     }
     const int rows_per_slab = slabs > 1 ? ((m / slabs + 255) / 256) * 256 : m;
     const size_t row_a = (size_t)(k / 2), row_c = (size_t)n * 4;
+    // The result (4 bytes per output) is what the bus spends its time on, so the first download should start as early as
+    // possible: the first row slab does not wait for all of B but takes it in kHostBParts blocks of rows, each followed by
+    // the product for those columns of C and their download, while the next block of B is still on its way up.
+    const int b_parts = (slabs > 1 && n >= 256 * kHostBParts) ? kHostBParts : 1;
+    const int cols_per_part = b_parts > 1 ? ((n / b_parts + 255) / 256) * 256 : n;
+    if (b_parts == 1 && b_bytes && (e = cudaMemcpyAsync(s.b, hB, b_bytes, cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return record_cuda_error(e, "cudaMemcpyAsync(B)");
     for (int i = 0, r0 = 0; r0 < m; ++i, r0 += rows_per_slab) {
         const int rows = (m - r0 < rows_per_slab) ? m - r0 : rows_per_slab;
         char *dA = static_cast<char *>(s.a) + (size_t)r0 * row_a;
@@ -442,6 +448,24 @@ int qm_gemm_s4_host(const void *hA, const void *hB, void *hC, int m, int n, int 
         if (row_a && (e = cudaMemcpyAsync(dA, static_cast<const char *>(hA) + (size_t)r0 * row_a, (size_t)rows * row_a,
                                           cudaMemcpyHostToDevice, stream)) != cudaSuccess)
             return record_cuda_error(e, "cudaMemcpyAsync(A)");
+        if (i == 0 && b_parts > 1) {
+            for (int j = 0, c0 = 0; c0 < n; ++j, c0 += cols_per_part) {
+                const int cols = (n - c0 < cols_per_part) ? n - c0 : cols_per_part;
+                char *dB = static_cast<char *>(s.b) + (size_t)c0 * row_a;
+                if (row_a && (e = cudaMemcpyAsync(dB, static_cast<const char *>(hB) + (size_t)c0 * row_a, (size_t)cols * row_a,
+                                                  cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+                    return record_cuda_error(e, "cudaMemcpyAsync(B)");
+                st = gemm_dispatch(dA, dB, dC + (size_t)c0 * 4, rows, cols, k, n, stream, nullptr);
+                if (st != QM_OK) return st;
+                cudaEvent_t ev = s.slab_done[kHostSlabs + j % kHostBParts];
+                if ((e = cudaEventRecord(ev, stream)) != cudaSuccess) return record_cuda_error(e, "cudaEventRecord");
+                if ((e = cudaStreamWaitEvent(s.copy_stream, ev, 0)) != cudaSuccess) return record_cuda_error(e, "cudaStreamWaitEvent");
+                if ((e = cudaMemcpy2DAsync(static_cast<char *>(hC) + (size_t)c0 * 4, row_c, dC + (size_t)c0 * 4, row_c, (size_t)cols * 4,
+                                           (size_t)rows, cudaMemcpyDeviceToHost, s.copy_stream)) != cudaSuccess)
+                    return record_cuda_error(e, "cudaMemcpy2DAsync(C)");
+            }
+            continue;
+        }
         st = gemm_dispatch(dA, s.b, dC, rows, n, k, n, stream, nullptr);
         if (st != QM_OK) return st;
         cudaStream_t out_stream = stream;

@@ -144,17 +144,31 @@ __device__ __forceinline__ bool mbar_spin_wait(uint32_t bar, uint32_t parity, vo
     return true;
 }
 
-// Whole-warp wait with one verdict for all lanes.  kRemote: lane 0 spins without suspending and the
-// shuffle that broadcasts its verdict also orders the other lanes behind its acquire.
+// Whole-warp wait with one verdict for all lanes.  kRemote: lane 0 alone spins (without suspending, cluster-scope acquire)
+// and broadcasts its verdict by shuffle; the other lanes make no acquire of their own, so this form is used only where what
+// follows does not read memory that the barrier guards: tcgen05.ld of an accumulator (ordered by tcgen05.fence) or stores into
+// a slot that the barrier declares free.
 template <bool kRemote>
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int lane)
 {
     if constexpr (!kRemote) {
-        // Every lane polls (each lane needs its own acquire of the data the barrier guards), but all lanes leave the
-        // loop in the same iteration.  One try_wait can answer differently for different lanes of a warp when the
-        // phase completes while the instruction is in flight; with a per-lane loop here, about one 8192^3 launch in
-        // 120 had a few stale TMEM lanes (the lowest lanes of a warp) behind the warp-wide .sync.aligned tcgen05.st /
-        // tcgen05.ld that follow such a wait.  With the uniform exit: none in 2000 launches.
+        // Every lane polls, and all lanes leave the loop in the same iteration.  Why both halves are needed:
+        //  * Visibility.  mbarrier.try_wait has acquire semantics for the thread that executes it and sees the phase
+        //    complete: the writes the barrier guards (TMA bytes counted by complete_tx, a peer's shared-memory stores
+        //    released by its arrive) are then visible to THAT thread.  A lane that only learned of the completion from a
+        //    vote or a shuffle has made no acquire of its own, so each lane must see `true` from its own try_wait.  The
+        //    loop ends only in an iteration in which every lane's own try_wait returned true.
+        //  * Convergence.  The instructions that follow such a wait are warp-wide .sync.aligned ones (tcgen05.ld,
+        //    tcgen05.st, tcgen05.wait), which require all 32 threads to execute the same instruction together; executed by
+        //    a diverged warp their behaviour is undefined.  One try_wait can answer differently for different lanes when
+        //    the phase completes while it is in flight, so a per-lane `while (!try_wait)` lets lanes leave in different
+        //    iterations, and nothing obliges the compiler to reconverge them before an inline-asm instruction it knows
+        //    nothing about.  __all_sync is a convergence point by definition: every lane that leaves the loop leaves it
+        //    from the same vote, so the warp is converged at the next instruction.  (With a per-lane loop about one
+        //    8192^3 launch in 120 had a few stale TMEM lanes, always the lowest lanes of one warp; with this form none.)
+        //  * Ordering against the tensor core's asynchronous accesses is not this function's job: every call site that
+        //    goes on to tcgen05.ld / tcgen05.st / tcgen05.mma issues tcgen05.fence::after_thread_sync after the wait, and
+        //    tcgen05.fence::before_thread_sync before the arrive that hands the data on.
         if (__all_sync(0xFFFFFFFFu, mbar_try_wait(bar, parity))) return true;
         const uint64_t t0 = globaltimer_ns();
         uint32_t spins = 0;
