@@ -59,10 +59,15 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 
 __device__ __forceinline__ uint32_t word(const uint4 &v, int s) { return s == 0 ? v.x : (s == 1 ? v.y : (s == 2 ? v.z : v.w)); }
 
-// PRE: B is the pre-laid-out form written by prelayout_kernel below, [block of 8 RG rows][round][warp][step][row group][lane]
+// MODE 1 (PRE): B is the pre-laid-out form written by prelayout_kernel below, [block of 8 RG rows][round][warp][step][row group][lane]
 // in 16-byte chunks: every load instruction of a warp reads 512 consecutive bytes, a warp's round is 4 KB and a CTA's round
-// 64 KB of consecutive addresses.
-template <int WARPS, int RG, int MS, bool PRE>
+// 64 KB of consecutive addresses.  MODE 2 (FULL): the plain layout of a B whose rows fill whole 32-row blocks and whose K fills
+// whole rounds (n % (8 RG) == 0, k % (128 WARPS MS) == 0): the same loads as MODE 0 without their bounds checks.  MODE 3 (WIDE,
+// MS == 2): such a B, 32-byte aligned, read with 256-bit loads: a warp takes two ADJACENT chunk steps of a round (256 elements
+// of K) and lane (g, q) loads chunks 2q and 2q + 1 of its row in one instruction, so that the four lanes of a row read one
+// whole 128-byte line where MODE 0 / 2 read 64 bytes of it; the rows of A are indexed by the same chunks, so every product
+// still pairs equal K indices.
+template <int WARPS, int RG, int MS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS == 16 ? 1 : 2))
 gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
                  uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
@@ -70,13 +75,17 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     using Cfg = RmmaCfg<WARPS, RG, MS>;
     constexpr int kWarps = Cfg::kWarps, kThreads = Cfg::kThreads, kRowGroups = Cfg::kRowGroups, kRowsPerCta = Cfg::kRowsPerCta,
                   kMaxSteps = Cfg::kMaxSteps;
+    constexpr bool PRE = MODE == 1, WIDE = MODE == 3, FULL = MODE == 2 || WIDE;
+    static_assert(!WIDE || MS == 2, "two chunks per 256-bit load");
     extern __shared__ uint4 smem_u4[];
     // The rows of A stay PACKED in shared memory, [16 tiles rows][chunks + 4] 16-byte units (the 64 bytes of padding put the two
     // rows a quarter-warp reads at once on different banks); the A fragments are split when they are read.
     uint4 *a_pk = smem_u4;
     const int chunks = k / 32;
     const int tiles = (m + 15) / 16;  // token tiles of 16 rows of A
-    const int pk_stride = chunks + 4;
+    // (WIDE reads chunks 2q + u: 32 bytes between the lanes of a row, so one chunk of padding puts the rows of a quarter-warp on
+    // different banks)
+    const int pk_stride = chunks + (WIDE ? 1 : 4);
     // [warp][row group][j][32]: accumulator register j of lane l at position (l + 4 (2 rg + (j & 1))) % 32, which makes both the
     // writes (one register of all lanes) and the reads (one token, 32 rows of B) hit 32 different banks
     int32_t *red = reinterpret_cast<int32_t *>(smem_u4 + (size_t)16 * tiles * pk_stride);
@@ -91,6 +100,12 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         return reinterpret_cast<const uint4 *>(B) + (((int64_t)rb * rounds_k + r) * kWarps + warp) * (32 * kMaxSteps * kRowGroups) + lane;
     };
 
+    // chunk of a row that this lane handles in step u of the round that starts at step t0 (t0 = warp + round * kWarps * kMaxSteps)
+    auto chunk_of = [&](int t0, int u) {
+        if constexpr (WIDE) return 4 * (t0 - warp) + 8 * warp + 2 * q + u;
+        else return 4 * (t0 + u * kWarps) + q;
+    };
+
     // L2 prefetch of one block of weights (this lane's share): returns no data, touches nothing the program can observe
     auto prefetch_block = [&](int rb) {
         if (rb >= num_blocks) return;
@@ -100,13 +115,11 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 for (int b = 0; b < kMaxSteps * kRowGroups * 512; b += 4096)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(pre_base(rb, r) - lane) + b + lane * 128));
         } else {
-            for (int t = warp; t < steps; t += kWarps) {
-                const int c = 4 * t + q;
-#pragma unroll
-                for (int rg = 0; rg < kRowGroups; ++rg) {
-                    const int row = rb * kRowsPerCta + rg * 8 + g;
-                    if (row < n && c < chunks) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)c * 16));
-                }
+            // every 128-byte line of the block exactly once: thread i takes line i % lines_per_row of row i / lines_per_row
+            const int lines_per_row = (int)((row_bytes + 127) / 128);
+            for (int i = threadIdx.x; i < kRowsPerCta * lines_per_row; i += kThreads) {
+                const int row = rb * kRowsPerCta + i / lines_per_row;
+                if (row < n) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)(i % lines_per_row) * 128));
             }
         }
     };
@@ -133,6 +146,15 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             for (int u = 0; u < kMaxSteps; ++u)
 #pragma unroll
                 for (int rg = 0; rg < kRowGroups; ++rg) w[u][rg] = __ldcs(src + 32 * (u * kRowGroups + rg));
+        } else if constexpr (WIDE) {
+#pragma unroll
+            for (int rg = 0; rg < kRowGroups; ++rg) {
+                const uint8_t *src = B + (int64_t)(rb * kRowsPerCta + rg * 8 + g) * row_bytes + (int64_t)chunk_of(t0, 0) * 16;
+                asm volatile("ld.global.cs.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(w[0][rg].x), "=r"(w[0][rg].y), "=r"(w[0][rg].z), "=r"(w[0][rg].w), "=r"(w[1][rg].x), "=r"(w[1][rg].y),
+                               "=r"(w[1][rg].z), "=r"(w[1][rg].w)
+                             : "l"(src));
+            }
         } else {
 #pragma unroll
             for (int u = 0; u < kMaxSteps; ++u) {
@@ -141,8 +163,12 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
 #pragma unroll
                 for (int rg = 0; rg < kRowGroups; ++rg) {
                     const int row = rb * kRowsPerCta + rg * 8 + g;
-                    w[u][rg] = make_uint4(0, 0, 0, 0);
-                    if (t < steps && c < chunks && row < n) w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                    if constexpr (FULL) {
+                        w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                    } else {
+                        w[u][rg] = make_uint4(0, 0, 0, 0);
+                        if (t < steps && c < chunks && row < n) w[u][rg] = __ldcs(reinterpret_cast<const uint4 *>(B + (int64_t)row * row_bytes) + c);
+                    }
                 }
             }
         }
@@ -152,10 +178,10 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
 #pragma unroll
         for (int u = 0; u < kMaxSteps; ++u) {
             const int t = t0 + u * kWarps;
-            const int c = 4 * t + q;
-            if (t < steps) {  // uniform over the warp
+            const int c = chunk_of(t0, u);
+            if (FULL || t < steps) {  // uniform over the warp (a whole round has every step)
                 uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
-                if (c < chunks) {
+                if (FULL || c < chunks) {
                     p0 = a_pk[(16 * tt + g) * pk_stride + c];
                     p1 = a_pk[(16 * tt + g + 8) * pk_stride + c];
                 }
@@ -275,11 +301,11 @@ __global__ void __launch_bounds__(256) prelayout_kernel(const uint8_t *__restric
     }
 }
 
-template <int WARPS, int RG, int MS, bool PRE>
+template <int WARPS, int RG, int MS, int MODE>
 static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 {
     using Cfg = RmmaCfg<WARPS, RG, MS>;
-    auto kernel = gemm_rmma_kernel<WARPS, RG, MS, PRE>;
+    auto kernel = gemm_rmma_kernel<WARPS, RG, MS, MODE>;
     const int tiles = (g.m + 15) / 16;
     const size_t smem = (size_t)16 * tiles * (g.k / 2 + 64) + Cfg::kRedBytes;  // packed rows of A, padded by 64 bytes
     static std::atomic<bool> configured[64];  // set once per device; a repeated cudaFuncSetAttribute is harmless
@@ -315,7 +341,14 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)
 {
     if (!rmma_eligible(g)) return QM_ERR_ARG;
-    return rmma_launch_cfg<16, 4, 2, false>(g, ctx);
+    // whole blocks of rows and whole rounds of K: the variant without bounds checks
+    static const int forced_mode = std::getenv("QM_RMMA_MODE") ? std::atoi(std::getenv("QM_RMMA_MODE")) : -1;
+    if (g.n % 32 == 0 && g.k % 4096 == 0 && forced_mode != 0) {
+        // 256-bit loads need 32-byte-aligned rows
+        if ((reinterpret_cast<uintptr_t>(g.B) & 31u) == 0 && forced_mode != 2) return rmma_launch_cfg<16, 4, 2, 3>(g, ctx);
+        return rmma_launch_cfg<16, 4, 2, 2>(g, ctx);
+    }
+    return rmma_launch_cfg<16, 4, 2, 0>(g, ctx);
 }
 
 // ---- offline weight pre-layout (optional) --------------------------------------------------------------------------
@@ -347,7 +380,7 @@ int prelayout_launch(const uint8_t *B, uint8_t *Bp, int n, int k, cudaStream_t s
 int rmma_launch_prelaid(const GemmArgs &g, const DeviceCtx &ctx)
 {
     if (!rmma_eligible(g)) return QM_ERR_ARG;
-    return rmma_launch_cfg<kPreWarps, kPreRG, kPreMS, true>(g, ctx);
+    return rmma_launch_cfg<kPreWarps, kPreRG, kPreMS, 1>(g, ctx);
 }
 
 }  // namespace qm
