@@ -763,6 +763,8 @@ def native_arm(args) -> None:
                 "d2h_bytes_per_step": int(hc.numel() * 4),
                 "ms_per_step": float(dt.item()) * 1e3,
                 "steps": e2e_steps,
+                # what bounds this figure: the bytes that cross PCIe per step, per GPU, over the step time (max over ranks)
+                "pcie_gbs_per_gpu": (ha.numel() + hb.numel() + hc.numel() * 4) / float(dt.item()) / 1e9,
                 "api": "qm_gemm_s4_host (pinned host A, B in; int32 C out; per GPU)",
                 "result_checksum": checksum,
                 "result_checksum_expected": expected,
