@@ -210,7 +210,12 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
     if (p.split_k > 1 && !(opts && opts->split_k) && through_scratch &&
         (tc_scratch_bytes_needed(m, n, p) > lc.scratch_bytes || tc_counters_needed(m, n, p) > lc.num_counters))
         p.split_k = 1;  // the table's choice does not fit the scratch: run unsplit rather than fail
-    if (p.stream_k == 2 && p.split_k < 2) p.stream_k = 0;  // a cluster of one partition is the plain form
+    if (is_dec && p.stream_k == 2 && !(opts && (opts->split_k || opts->stream_k))) {
+        // the table sized the cluster for a typical device; this device may hold fewer clusters of that size at once
+        const int tiles = ((n + 127) / 128) * ((m + p.tile_n - 1) / p.tile_n);
+        for (int cap; p.split_k >= 2 && (cap = dec_cluster_capacity(ctx->device, p.tile_n, p.split_k)) > 0 && tiles > cap;) --p.split_k;
+    }
+    if (p.stream_k == 2 && p.split_k < 2) p.stream_k = 0, p.split_k = 1;  // a cluster of one partition is the plain form
     if (is_dec) {
         if ((p.tile_n != 16 && p.tile_n != 32 && p.tile_n != 64) || p.cta_pair != 1) return QM_ERR_ARG;
         st = dec_launch(g, p, lc);

@@ -28,6 +28,7 @@
 //
 // Launches chain through programmatic dependent launch: set-up overlaps the previous kernel's tail and
 // global memory is touched only after griddepcontrol.wait.  All waits are bounded as in gemm_tc_kernel.
+#include <atomic>
 #include <cuda.h>
 
 #include <cstdio>
@@ -679,10 +680,49 @@ int launch_one(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool balanc
     return QM_OK;
 }
 
+// g_cluster_cap[device][log2(BN / 16)][size - 2]: clusters of `size` CTAs of the cluster form that the device runs at once
+std::atomic<int> g_cluster_cap[64][3][3];
+
+template <int BN>
+void query_cluster_capacity(int device)
+{
+    for (int size = 2; size <= 4; ++size) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(size * 64), 1, 1);
+        cfg.blockDim = dim3(kNumThreads, 1, 1);
+        cfg.dynamicSmemBytes = DecCfg<BN, 1, true>::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_dec_kernel<BN, 1, true>, &cfg) != cudaSuccess) {
+            cudaGetLastError();  // not fatal: the table's estimate stays in force
+            clusters = 0;
+        }
+        g_cluster_cap[device & 63][BN == 16 ? 0 : (BN == 32 ? 1 : 2)][size - 2].store(clusters, std::memory_order_release);
+    }
+}
+
 }  // namespace
+
+int dec_cluster_capacity(int device, int tile_n, int size)
+{
+    if (size < 2 || size > 4 || (tile_n != 16 && tile_n != 32 && tile_n != 64)) return 0;
+    return g_cluster_cap[device & 63][tile_n == 16 ? 0 : (tile_n == 32 ? 1 : 2)][size - 2].load(std::memory_order_acquire);
+}
 
 int dec_prepare_device()
 {
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess) {
+        query_cluster_capacity<16>(device);
+        query_cluster_capacity<32>(device);
+        query_cluster_capacity<64>(device);
+    }
     int st = prepare_one<16, 1, false>();
     if (st == QM_OK) st = prepare_one<32, 1, false>();
     if (st == QM_OK) st = prepare_one<64, 1, false>();

@@ -13,7 +13,8 @@
 // and one store per output finish a row of B.
 //
 // The accumulators hold 256 x the true sums (K < 131072 keeps them inside int32, as on the tensor path).  Launches
-// chain through programmatic dependent launch like the decode kernel's.
+// chain through programmatic dependent launch like the decode kernel's: before the grid dependency is resolved a warp
+// only issues L2 prefetches for its first rows of B (a prefetch returns no data).
 #include <atomic>
 #include <cstdlib>
 
@@ -41,7 +42,21 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
     ptx::grid_launch_dependents();
     const int chunks = k / 32;  // 16-byte packed chunks per row
     const int64_t row_bytes = k / 2;
-    ptx::grid_dependency_wait();  // nothing above touched global memory
+    constexpr int kRowsPerStep = RU;
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int num_warps = gridDim.x * kWarps;
+    const int first_row0 = warp * kRowsPerStep;
+    // rows past the end re-read the step's first row; their results are not stored
+    auto row_ptr = [&](int row0, int u) { return reinterpret_cast<const uint4 *>(B + (int64_t)(row0 + u < n ? row0 + u : row0) * row_bytes); };
+    if (first_row0 < n) {
+        // L2 prefetch of this warp's first rows: returns no data, so it may run before the grid dependency is resolved
+#pragma unroll
+        for (int u = 0; u < kRowsPerStep; ++u)
+            for (int64_t b = (int64_t)lane * 128; b < row_bytes; b += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(row_ptr(first_row0, u)) + b));
+    }
+    ptx::grid_dependency_wait();  // nothing above read or wrote global memory
 
     for (int i = threadIdx.x; i < MR * chunks; i += kThreads) {
         const int r = i / chunks, c = i - r * chunks;
@@ -54,25 +69,17 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
     }
     __syncthreads();
 
-    constexpr int kRowsPerStep = RU;
-    const int lane = threadIdx.x & 31;
-    const int warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
-    const int num_warps = gridDim.x * kWarps;
-    for (int row0 = warp * kRowsPerStep; row0 < n; row0 += num_warps * kRowsPerStep) {
+    for (int row0 = first_row0; row0 < n; row0 += num_warps * kRowsPerStep) {
         int acc[kRowsPerStep][MR];
 #pragma unroll
         for (int u = 0; u < kRowsPerStep; ++u)
 #pragma unroll
             for (int r = 0; r < MR; ++r) acc[u][r] = 0;
-        const uint4 *brow[kRowsPerStep];  // rows past the end re-read the step's first row; their results are not stored
+        const uint4 *brow[kRowsPerStep];
 #pragma unroll
-        for (int u = 0; u < kRowsPerStep; ++u)
-            brow[u] = reinterpret_cast<const uint4 *>(B + (int64_t)(row0 + u < n ? row0 + u : row0) * row_bytes);
-#pragma unroll(8 / kRowsPerStep)
-        for (int c = lane; c < chunks; c += 32) {
-            uint4 w[kRowsPerStep];
-#pragma unroll
-            for (int u = 0; u < kRowsPerStep; ++u) w[u] = __ldcs(brow[u] + c);
+        for (int u = 0; u < kRowsPerStep; ++u) brow[u] = row_ptr(row0, u);
+        // acc += (chunk c of the rows of A) x (chunk c of the step's rows of B, already in registers)
+        auto accumulate = [&](int c, const uint4(&w)[kRowsPerStep]) {
             uint4 wl[kRowsPerStep], wh[kRowsPerStep];
 #pragma unroll
             for (int u = 0; u < kRowsPerStep; ++u) tc::split_s4x32(w[u], wl[u], wh[u]);
@@ -93,6 +100,13 @@ gemv_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_
                     acc[u][r] = s;
                 }
             }
+        };
+#pragma unroll(8 / kRowsPerStep)
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 w[kRowsPerStep];
+#pragma unroll
+            for (int u = 0; u < kRowsPerStep; ++u) w[u] = __ldcs(brow[u] + c);
+            accumulate(c, w);
         }
 #pragma unroll
         for (int u = 0; u < kRowsPerStep; ++u)

@@ -84,6 +84,8 @@ int dequant_launch(const int32_t *acc, int64_t ld_acc, const float *scale_a, con
 
 // qm_gemm_dec.cu: decode form (swap_ab, tile_n 16/32/64), B rows through TMEM; split-K through the context's scratch
 int dec_prepare_device();
+// clusters of `size` (2..4) CTAs of the decode kernel's cluster form that `device` runs at once; 0 = the driver did not say
+int dec_cluster_capacity(int device, int tile_n, int size);
 int dec_launch(const GemmArgs &g, const TcPlan &p, const DeviceCtx &ctx);
 
 // qm_gemv.cu: one to four rows of A, weight streaming with dp4a (no tensor cores); int32 or fused bf16 output

@@ -87,6 +87,16 @@ inline bool tc_eligible(const GemmArgs &g)
     return g.k % 32 == 0 && g.k < 131072 && aligned16(g.A) && aligned16(g.B);
 }
 
+// Clusters of `size` CTAs (one CTA per SM) that run at once.  A cluster sits inside one GPC, so GPCs whose SM count is not
+// a multiple of the size leave SMs unused: measured on B200 (148 SMs), 74 clusters of 2, 44 of 3, 32 of 4.  The dispatcher
+// replaces this estimate by the driver's answer for the device at hand (dec_cluster_capacity).
+inline int cluster_slots(int size, int num_sms)
+{
+    if (size <= 1) return num_sms;
+    if (size == 2) return num_sms / 2;
+    return size == 3 ? num_sms * 11 / 37 : num_sms * 8 / 37;
+}
+
 inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
     TcPlan p{256, 0, 1, 1, 0, 0, 1};
@@ -112,6 +122,12 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
         // thread-block cluster and add up through its shared memory (32 x 4096 x 4096: 10.6 -> 9.1 us, 64 x 4096 x 4096:
         // 13.7 -> 11.4 us, 64 x 8192 x 8192: 18.5 -> 16.7 us).  With 16 tokens the scratch path is as fast (7.9 vs 8.1 us).
         if (p.tile_n >= 32 && p.split_k >= 2) p.stream_k = 2;
+        if (p.stream_k == 2) {
+            // One tile more than the device holds clusters and the launch takes two rounds (64 x 6144 x 4096, 48 tiles:
+            // 23.5 us as clusters of 3, 12.6 us as clusters of 2): take the largest cluster that fits.
+            while (p.split_k >= 2 && tiles > cluster_slots(p.split_k, num_sms)) --p.split_k;
+            if (p.split_k < 2) p.stream_k = 0, p.split_k = 1;
+        }
         if (p.tile_n == 16 && tiles > num_sms / 2) {
             // Enough tiles to put two smaller CTAs on every SM, which hide each other's pipeline bubbles:
             // 16 x 11008 x 4096 (86 tiles) 11.6 -> 10.3 us with 3 K partitions, 16 x 28672 x 8192 (224 tiles)

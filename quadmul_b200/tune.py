@@ -80,7 +80,7 @@ def time_variant(qm, torch, m, n, k, opts, iters, per_graph):
 
 # Shapes of the kernel-family sweep behind the decode cost model: rows of A x (N, K) of common layer shapes.
 FAMILY_M = [1, 2, 4, 8, 16, 24, 32, 48, 64]
-FAMILY_NK = [(2048, 4096), (4096, 4096), (6144, 4096), (8192, 4096), (11008, 4096), (16384, 4096), (28672, 4096), (2048, 8192),
+FAMILY_NK = [(2048, 4096), (4096, 4096), (6144, 4096), (8192, 4096), (11008, 4096), (12288, 4096), (14336, 4096), (16384, 4096), (22016, 4096), (28672, 4096), (2048, 8192),
              (4096, 8192), (8192, 8192), (10240, 8192), (28672, 8192), (57344, 8192), (4096, 2048), (4096, 11008), (4096, 14336)]
 FAMILIES = {"rmma": dict(kernel=4), "gemv": dict(kernel=3), "dec": dict(kernel=1)}  # dec: the tensor path with the table's K cut
 
