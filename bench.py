@@ -511,6 +511,29 @@ def multi_gpu_legs(torch, dist, qm, world: int, rank: int, steps: int = 2) -> di
 # ------------------------------------------------------------------------------------------
 # native arm
 # ------------------------------------------------------------------------------------------
+def bind_host_to_gpu_numa_node(torch, device_index: int):
+    """Restrict this process to the CPUs next to the GPU (sysfs `local_cpulist` of its PCI function), so that host buffers
+    allocated from now on land on that NUMA node (first touch).  Returns (node, previous affinity) or (None, None) when sysfs
+    does not say; undo with os.sched_setaffinity(0, previous)."""
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bdf}"
+        node = int(open(f"{base}/numa_node").read().strip())
+        cpus = set()
+        for part in open(f"{base}/local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        previous = os.sched_getaffinity(0)
+        cpus &= previous
+        if node < 0 or not cpus:
+            return None, None
+        os.sched_setaffinity(0, cpus)
+        return node, previous
+    except (OSError, ValueError, AttributeError):
+        return None, None
+
+
 def free_port() -> int:
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -733,6 +756,7 @@ def native_arm(args) -> None:
 
     # ---- end to end through the host-buffer C-ABI call, copies inside the timed region ----
     if not args.no_e2e and not large:
+        numa_node, previous_affinity = (None, None) if args.no_numa_bind else bind_host_to_gpu_numa_node(torch, torch.cuda.current_device())
         ha = a.cpu().pin_memory()
         hb = bs[0].cpu().pin_memory()
         hc = torch.empty((m, n_local), dtype=torch.int32).pin_memory()
@@ -746,6 +770,8 @@ def native_arm(args) -> None:
         dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        if previous_affinity:
+            os.sched_setaffinity(0, previous_affinity)
         if rank == 0:
             import numpy as np
 
@@ -766,6 +792,7 @@ def native_arm(args) -> None:
                 # what bounds this figure: the bytes that cross PCIe per step, per GPU, over the step time (max over ranks)
                 "pcie_gbs_per_gpu": (ha.numel() + hb.numel() + hc.numel() * 4) / float(dt.item()) / 1e9,
                 "api": "qm_gemm_s4_host (pinned host A, B in; int32 C out; per GPU)",
+                "host_numa_node": numa_node,  # rank 0's; every rank binds its host buffers to the node of its own GPU (None: not bound)
                 "result_checksum": checksum,
                 "result_checksum_expected": expected,
                 "result_checksum_of": f"every 65537th element of the host C ({len(pos)} elements), expected value from the CPU oracle",
@@ -846,6 +873,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-numa-bind", action="store_true", help="end-to-end leg: leave the host buffers wherever the process happens to run")
     ap.add_argument("--no-extra", action="store_true", help="skip the further shapes (1 GPU) and the sharded check / 32768^3 legs (2+ GPUs)")
     ap.add_argument("--shape", default=None, help="M,N,K of a single-GPU case other than the headline one (profiling, sweeps)")
     ap.add_argument("--tile-n", type=int, default=0)

@@ -172,9 +172,12 @@ def test_row_kernel_for_one_to_four_rows(qm, cuda_clean, oracle, golden, m):
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 17, 32, 40, 64])
 def test_register_resident_mma_kernel(qm, cuda_clean, oracle, m):
     """gemm_rmma_kernel (weights straight into registers, mma.sync s8): forced with kernel=4.  Row counts that are not a
-    multiple of 32, K below one step per warp, K that is not a multiple of 128, the K limit, several blocks per CTA."""
+    multiple of 32, K below one step per warp, K that is not a multiple of 128, the K limit, several blocks per CTA (the
+    rounds after the first then come through the cp.async ring in shared memory: two buffers, or one at 33-48 rows of A), also
+    with two rounds of K per block and a ragged last round."""
     torch = cuda_clean
-    for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (37, 96), (64, 8192), (300, 1056), (20000, 256)):
+    for n, k in ((4096, 4096), (11008, 4096), (1001, 32), (37, 96), (64, 8192), (300, 1056), (20000, 256), (6016, 8192), (9500, 4128),
+                 (28672, 4096)):
         if m > 16 and k > 4096:  # several 16-row tiles of A need the weights of a block resident in registers
             continue
         ap = oracle.fill_packed(m, k, 93); bp = oracle.fill_packed(n, k, 94)
