@@ -57,10 +57,12 @@ typedef struct qm_gemm_opts {
                        the decode kernel                                                          */
     int plain_stores; /* 1 = write C with ordinary vector stores only (no TMA store); for a C that lives in
                          another GPU's memory (peer mapping), as the fused gather of the sharded driver uses */
-    int stream_k;   /* decode kernel only, how K is cut and the partial tiles meet: 0 = table, 1 = split_k partitions
+    int stream_k;   /* how K is cut and the partial tiles meet.  Decode kernel: 0 = table, 1 = split_k partitions
                        per tile summed through scratch memory, 2 = one equal contiguous share of the (tile, K) work
                        per CTA summed through scratch memory, 3 = split_k (2..4) partitions per tile, one CTA each in
-                       one thread-block cluster, summed through the cluster's shared memory            */
+                       one thread-block cluster, summed through the cluster's shared memory.  Large-shape kernel
+                       (256 x 256 pair tile): 0 = table, 1 = whole tiles only, 2 = when the last round of whole tiles
+                       over the CTA pairs is short, its tiles run as K partitions that add into zeroed tiles */
     int ctas_per_sm; /* decode kernel only: 0 = table, 1 = one CTA per SM with the whole shared memory as its ring,
                         2 = two smaller CTAs per SM (tile_n 16 only)                                  */
 } qm_gemm_opts_t;

@@ -192,7 +192,8 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
         if (opts->stream_k < 0 || opts->stream_k > 3) return QM_ERR_ARG;
         if (opts->stream_k) p.stream_k = opts->stream_k - 1;
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k) p.stream_k = 0;
-        if (p.stream_k && !(p.a_tmem && p.swap_ab)) return QM_ERR_ARG;  // only the decode kernel has it
+        // the decode kernel has all three forms; the large-shape kernel takes 2 as "cut a short last round of tiles into K partitions"
+        if (p.stream_k && !(p.a_tmem && p.swap_ab) && !(p.a_tmem && !p.swap_ab && p.stream_k == 1)) return QM_ERR_ARG;
         if (opts->ctas_per_sm < 0 || opts->ctas_per_sm > 2) return QM_ERR_ARG;
         if (opts->ctas_per_sm) p.ctas_per_sm = opts->ctas_per_sm;
         else if (opts->swap_ab || opts->tile_n || opts->cta_pair || opts->a_tmem || opts->split_k || opts->stream_k) p.ctas_per_sm = 1;
@@ -231,7 +232,8 @@ int gemm_dispatch(const void *A, const void *B, void *C, int m, int n, int k, in
             if (opts && opts->split_k) return QM_ERR_ALIGN;
             p.split_k = 1;
         }
-        return tc2_launch(g, lc, p.split_k);
+        static const bool allow_tail = !std::getenv("QM_TC2_NO_TAIL");
+        return tc2_launch(g, lc, p.split_k, allow_tail && p.stream_k == 1 && p.split_k == 1 && tc2_can_split(g));
     }
     return tc_launch(g, p, lc);
 }

@@ -34,6 +34,7 @@
 #include "qm_internal.h"
 #include "qm_ptx.cuh"
 #include "qm_tc_common.cuh"
+#include "qm_tile_table.h"
 
 namespace qm {
 
@@ -128,7 +129,8 @@ template <int H, bool MC, bool DQ>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                 const __grid_constant__ CUtensorMap tmapC, int use_tma_store, int32_t *__restrict__ C, int64_t ldc, int M,
-                int N, int K, int *status, int split_k, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
+                int N, int K, int *status, int split_k, int tail_tiles, int tail_split, const float *__restrict__ scale_a,
+                const float *__restrict__ scale_b)
 {
     using Cfg = Tc2Cfg<H>;
     constexpr int S = Cfg::S, SP = Cfg::SP;
@@ -152,11 +154,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     const uint32_t cta_rank = cluster_ctarank();
     const int unit = (int)(blockIdx.x >> 1), num_units = (int)(gridDim.x >> 1);
     const int tilesP = (M + 255) / 256, tilesQ = (N + kBN - 1) / kBN;
-    // A work item is one K partition of one tile; with split_k > 1 the partitions add into a C the host zeroed.
-    const int num_tiles = tilesP * tilesQ * split_k;
+    // A work item is one K partition of one tile.  All tiles but the last tail_tiles of the static order are cut into
+    // split_k partitions, the last tail_tiles (the ones that would leave most CTA pairs idle in a last round of whole tiles)
+    // into tail_split; where a tile has more than one partition they add into a C that the host zeroed.
+    const int tiles_all = tilesP * tilesQ;
+    const int head_items = (tiles_all - tail_tiles) * split_k;
+    const int num_tiles = head_items + tail_tiles * tail_split;  // work items
     const int num_kb_total = (K + H * kSubK - 1) / (H * kSubK);  // stages per tile; TMA zero-fills beyond K
-    auto kb_begin = [&](int item) { return (int)(((long long)(item % split_k) * num_kb_total) / split_k); };
-    auto kb_end = [&](int item) { return (int)(((long long)(item % split_k + 1) * num_kb_total) / split_k); };
+    auto item_tile = [&](int item) { return item < head_items ? item / split_k : tiles_all - tail_tiles + (item - head_items) / tail_split; };
+    auto item_parts = [&](int item) { return item < head_items ? split_k : tail_split; };
+    auto item_part = [&](int item) { return item < head_items ? item % split_k : (item - head_items) % tail_split; };
+    auto kb_begin = [&](int item) { return (int)(((long long)item_part(item) * num_kb_total) / item_parts(item)); };
+    auto kb_end = [&](int item) { return (int)(((long long)(item_part(item) + 1) * num_kb_total) / item_parts(item)); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SP; ++s) {
@@ -197,7 +206,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             bool ok = true;
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
-                tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
+                tile_coords(item_tile(t), tilesP, tilesQ, tp, tq);
                 const int yA = tp * 256 + (int)cta_rank * kRowsA;
                 const int yB = tq * kBN + (int)cta_rank * kRowsB;
                 for (int kb = kb_begin(t), kbe = kb_end(t); kb < kbe; ++kb, ++it) {
@@ -283,7 +292,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         bool buf_used = false;
         for (int t = unit; t < num_tiles; t += num_units, ++lt) {
             int tp, tq;
-            tile_coords(t / split_k, tilesP, tilesQ, tp, tq);
+            tile_coords(item_tile(t), tilesP, tilesQ, tp, tq);
             const bool ok = warp_wait<false>(acc_full, lt & 1u, abort_flag, lane);
             if (!ok) {
                 if (lane == 0) {
@@ -296,13 +305,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
             const int row0 = tp * 256 + (int)cta_rank * kRowsA + quarter * 32;
             const int q0 = tq * kBN + half * 128;
+            const bool reduce_add = item_parts(t) > 1;
             auto store = [&](const uint32_t(&v)[32], int col) {
                 if (use_tma_store) {
                     if (buf_used) {
                         if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the buffer
                         __syncwarp();
                     }
-                    store_block_tma(v, buf, lane, &tmapC, col, row0, false, split_k > 1);
+                    store_block_tma(v, buf, lane, &tmapC, col, row0, false, reduce_add);
                     buf_used = true;
                 } else {
                     uint32_t h0[16], h1[16];
@@ -478,8 +488,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     }
 }
 
+// Zeroes the last tail_tiles 256 x 256 tiles of the static order in C (eight blocks of 32 rows per tile): the K partitions of
+// those tiles add into them with TMA reduce-add.  C is 16-byte aligned with a row pitch of whole 16 bytes.
+__global__ void __launch_bounds__(256) zero_tail_tiles_kernel(int32_t *__restrict__ C, int64_t ldc, int M, int N, int tail_tiles)
+{
+    const int tilesP = (M + 255) / 256, tilesQ = (N + kBN - 1) / kBN;
+    int tp, tq;
+    tile_coords(tilesP * tilesQ - tail_tiles + (int)(blockIdx.x >> 3), tilesP, tilesQ, tp, tq);
+    const int row = tp * 256 + (int)(blockIdx.x & 7) * 32 + (int)(threadIdx.x >> 3);
+    if (row >= M) return;
+    int32_t *dst = C + (int64_t)row * ldc;
+    for (int col = tq * kBN + (int)(threadIdx.x & 7) * 4; col < (tq + 1) * kBN && col < N; col += 32) {
+        if (col + 4 <= N) {
+            *reinterpret_cast<int4 *>(dst + col) = make_int4(0, 0, 0, 0);
+        } else {
+            for (int c = col; c < N; ++c) dst[c] = 0;
+        }
+    }
+}
+
 template <int H, bool MC, bool DQ>
-int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
+int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool split_tail)
 {
     auto kernel = gemm_tc2_kernel<H, MC, DQ>;
     const int64_t kbytes = g.k / 2;
@@ -540,9 +569,19 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
     if (cached < units) units = cached;
     if (units < 1) units = 1;
     if (tiles < units) units = (int)tiles;
+    // Whole tiles in rounds over the pairs leave a last round of `rest` tiles with most pairs idle.  When at least two K
+    // partitions per tile of that round fit the pairs, they run as partitions that add into the zeroed tiles instead: the last
+    // round then takes a fraction of a tile's main loop plus one epilogue (1024 x 10240 x 8192, 160 tiles on 74 pairs: 12 tiles
+    // as 6 partitions each).
+    int tail_tiles = 0, tail_split = 1;
+    if (split_tail && !DQ && split_k == 1 && use_tma_store && tc2_tail_plan(tiles, units, num_kb, &tail_tiles, &tail_split)) {
+        zero_tail_tiles_kernel<<<(unsigned)(tail_tiles * 8), 256, 0, g.stream>>>(g.C, g.ldc, g.m, g.n, tail_tiles);
+        cudaError_t ze = cudaPeekAtLastError();
+        if (ze != cudaSuccess) return record_cuda_error(ze, "zero_tail_tiles_kernel launch");
+    }
     cfg.gridDim = dim3((unsigned)(units * 2), 1, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k, g.scale_a,
-                                       g.scale_b);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k, tail_tiles,
+                                       tail_split, g.scale_a, g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_tc2_kernel launch");
     return QM_OK;
 }
@@ -569,9 +608,9 @@ bool tc2_can_split(const GemmArgs &g)
     return !g.plain_stores && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && !std::getenv("QM_NO_TMA_STORE");
 }
 
-int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k)
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool split_tail)
 {
-    return tc2_launch_variant<2, true, false>(g, ctx, split_k);
+    return tc2_launch_variant<2, true, false>(g, ctx, split_k, split_tail);
 }
 
 bool tc2_can_dequant(const GemmArgs &g)
@@ -581,7 +620,7 @@ bool tc2_can_dequant(const GemmArgs &g)
 
 int tc2_launch_dequant(const GemmArgs &g, const DeviceCtx &ctx)
 {
-    return tc2_launch_variant<2, true, true>(g, ctx, 1);
+    return tc2_launch_variant<2, true, true>(g, ctx, 1, false);
 }
 
 }  // namespace qm

@@ -73,7 +73,8 @@ int tc_counters_needed(int m, int n, const TcPlan &p);
 
 // qm_gemm_tc2.cu: 256 x 256 pair tile, A through TMEM
 int tc2_prepare_device();
-int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k);
+// split_tail: a short last round of whole tiles may run as K partitions of its tiles (tc2_tail_plan); needs tc2_can_split
+int tc2_launch(const GemmArgs &g, const DeviceCtx &ctx, int split_k, bool split_tail);
 bool tc2_can_split(const GemmArgs &g);  // K partitions accumulate through TMA reduce-add: needs an aligned local C
 bool tc2_can_dequant(const GemmArgs &g);  // the fused bf16 epilogue stores with TMA only: aligned out, ldc % 8 == 0
 int tc2_launch_dequant(const GemmArgs &g, const DeviceCtx &ctx);

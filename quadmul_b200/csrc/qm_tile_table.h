@@ -97,6 +97,22 @@ inline int cluster_slots(int size, int num_sms)
     return size == 3 ? num_sms * 11 / 37 : num_sms * 8 / 37;
 }
 
+// The last round of whole 256 x 256 tiles over `units` CTA pairs holds tiles % units tiles.  When every one of them can be
+// cut into at least two K partitions without exceeding the pairs (and a partition keeps at least two stages), that round runs
+// as partitions instead: *tail_tiles tiles in *tail_split parts each.  Returns false when the tile list is left as it is.
+inline bool tc2_tail_plan(int64_t tiles, int units, int stages, int *tail_tiles, int *tail_split)
+{
+    *tail_tiles = 0, *tail_split = 1;
+    if (units < 1 || tiles <= units) return false;
+    const int rest = (int)(tiles % units);
+    int parts = rest > 0 ? units / rest : 0;
+    if (parts > 8) parts = 8;
+    if (parts > stages / 2) parts = stages / 2;
+    if (parts < 2) return false;
+    *tail_tiles = rest, *tail_split = parts;
+    return true;
+}
+
 inline TcPlan plan_tc(int m, int n, int k, int num_sms)
 {
     TcPlan p{256, 0, 1, 1, 0, 0, 1};
@@ -165,6 +181,10 @@ inline TcPlan plan_tc(int m, int n, int k, int num_sms)
                 if (sk > stages / 2) sk = stages / 2;
                 p.split_k = sk < 1 ? 1 : sk;
             }
+            // More tiles than pairs: a short last round is cut into K partitions (stream_k = 1 here means "split the
+            // tail"; the launch decides with the number of pairs the device really runs at once).
+            int tail_tiles, tail_split;
+            if (p.split_k == 1 && tc2_tail_plan(tiles, pairs, stages, &tail_tiles, &tail_split)) p.stream_k = 1;
         }
     }
     return p;

@@ -1,14 +1,15 @@
 """The reference's benchmark loop on its own shape list, with this library behind `quadmul.gemm`.
 
-    python -m quadmul_b200.shapes_bench [--all] [--runs 50]
+    python -m quadmul_b200.shapes_bench [--all] [--runs 50] [--nk N,K]
 
 Mirrors the reference's test script (test.py:18-127, shape list test.py:130-187): for every (M, N, K) it packs
 random int4 operands, checks `quadmul.gemm` against `torch._int_mm` on the unpacked int8 values (the reference
 accepts a difference of 1, test.py:43; here the results must be equal), then times three CUDA graphs of `runs`
 launches each -- cuBLASLt int8 (`torch._int_mm`), `quadmul.gemm`, and fp16 `torch.matmul` -- and prints one markdown
 row per shape in the layout of the reference's benchmarks/*.md.  Differences from the reference's method:
-CUDA events instead of host wall clock, the best of 5 replays instead of one, values drawn from [-8, 7] instead
-of [-8, 6].  `--all` adds the nine shapes the reference lists but comments out (M = 128 and M = 4096 rows).
+CUDA events instead of host wall clock, the best of 5 replays instead of one with the three candidates' replays taken in
+turn (same clock and power state for all), values drawn from [-8, 7] instead of [-8, 6].  `--all` adds the nine shapes
+the reference lists but comments out (M = 128 and M = 4096 rows).
 """
 from __future__ import annotations
 
@@ -22,7 +23,7 @@ ACTIVE_M = {  # test.py:130-187: which M values are active per (N, K) block
 }
 
 
-def time_graph(torch, fn, runs):
+def make_graph(torch, fn, runs):
     fn()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -31,15 +32,23 @@ def time_graph(torch, fn, runs):
             fn()
     g.replay()
     torch.cuda.synchronize()
-    best = 1e30
-    for _ in range(5):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        best = min(best, e0.elapsed_time(e1) / runs)
-    return best * 1e-3
+    return g
+
+
+def time_graphs_interleaved(torch, graphs, runs, rounds=5):
+    """Best time per launch of every graph, the replays of the candidates taken in turn (and the turn order rotated) so that
+    all of them see the same clock and power state: on a 1 kW part a candidate timed after another's long run starts hotter."""
+    best = [1e30] * len(graphs)
+    for r in range(rounds):
+        for j in range(len(graphs)):
+            i = (j + r) % len(graphs)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graphs[i].replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best[i] = min(best[i], e0.elapsed_time(e1) / runs)
+    return [b * 1e-3 for b in best]
 
 
 def main():
@@ -50,13 +59,17 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--runs", type=int, default=50)
+    ap.add_argument("--nk", default=None, help="only this (N, K) block of the list, e.g. 10240,8192")
     args = ap.parse_args()
     import quadmul_b200
 
     quadmul_b200.init()
     print("| M | N | K | cuBLAS int8 TOPS | quadmul_b200 TOPS | cuBLAS fp16 TOPS | vs int8 | vs fp16 | exact |")
     print("|---|---|---|---|---|---|---|---|---|")
+    only = tuple(int(x) for x in args.nk.split(",")) if args.nk else None
     for n, k in NK:
+        if only and (n, k) != only:
+            continue
         ms = [128, 256, 512, 1024, 2048, 4096] if args.all else ACTIVE_M[(n, k)]
         for m in ms:
             a8 = torch.randint(-8, 8, (m, k), dtype=torch.int8, device="cuda")
@@ -72,9 +85,11 @@ def main():
             bh = torch.randn((n, k), dtype=torch.float16, device="cuda")
             ch = torch.zeros((m, n), dtype=torch.float16, device="cuda")
             runs = args.runs if 2.0 * m * n * k < 4e12 else 10
-            t8 = time_graph(torch, lambda: torch._int_mm(a8, b8.t(), out=c_ref), runs)
-            tq = time_graph(torch, lambda: quadmul.gemm(a, b, c, m, n, k), runs)
-            th = time_graph(torch, lambda: torch.matmul(ah, bh.t(), out=ch), runs)
+            graphs = [make_graph(torch, lambda: torch._int_mm(a8, b8.t(), out=c_ref), runs),
+                      make_graph(torch, lambda: quadmul.gemm(a, b, c, m, n, k), runs),
+                      make_graph(torch, lambda: torch.matmul(ah, bh.t(), out=ch), runs)]
+            t8, tq, th = time_graphs_interleaved(torch, graphs, runs)
+            del graphs
             ops = 2.0 * m * n * k / 1e12
             print(f"| {m} | {n} | {k} | {ops / t8:.0f} | {ops / tq:.0f} | {ops / th:.0f} | {t8 / tq:.2f}x | {th / tq:.2f}x | {exact} |", flush=True)
             del a8, b8, a, b, c, c_ref, ah, bh, ch

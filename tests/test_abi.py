@@ -93,6 +93,9 @@ def test_plan(qm):
     # clusters of K partitions: the largest size of which the device holds as many as there are tiles
     assert qm.plan(64, 6144, 8192)["stream_k"] == 3 and qm.plan(64, 6144, 8192)["split_k"] == 2   # 48 tiles: 3 would not fit
     assert qm.plan(64, 5120, 8192)["split_k"] == 3 and qm.plan(64, 4608, 8192)["split_k"] == 3    # 40 and 36 tiles
+    # 160 tiles on 74 CTA pairs: the 12 tiles of the third round run as K partitions; 8192^3 (62 tiles in the last round) does not
+    assert qm.plan(1024, 10240, 8192)["stream_k"] == 2 and qm.plan(1024, 10240, 8192)["split_k"] == 1
+    assert qm.plan(8192, 8192, 8192)["stream_k"] == 1 and qm.plan(2048, 4096, 4096)["stream_k"] == 1
     assert qm.plan(5, 7, 30)["kernel"] == _lib.QM_KERNEL_SIMT      # k % 32 != 0
     assert qm.plan(8, 8, 131072)["kernel"] == _lib.QM_KERNEL_SIMT  # 256 x sum would leave int32
     with pytest.raises(qm.QuadmulError):
@@ -126,7 +129,9 @@ def test_plan_is_consistent_over_a_grid_of_shapes(qm):
                         assert p["tile_n"] >= 32 and 2 <= p["split_k"] <= 4 and p["ctas_per_sm"] == 1
                     assert p["ctas_per_sm"] == 1 or (p["ctas_per_sm"] == 2 and p["tile_n"] == 16)
                 else:
-                    assert p["stream_k"] == 1 and p["ctas_per_sm"] == 1
+                    assert p["ctas_per_sm"] == 1
+                    # the large-shape kernel may cut a short last round of whole tiles into K partitions (reported as stream_k = 2)
+                    assert p["stream_k"] == 1 or (p["stream_k"] == 2 and tm and pair and p["split_k"] == 1)
                 if tm and not swap:
                     assert pair and p["tile_n"] == 256
                 if pair:

@@ -546,9 +546,40 @@ def test_square_8192_slab_points_and_properties(qm, cuda_clean, oracle):
     assert torch.equal(c, c2)
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (1024, 10240, 1024),   # 160 tiles on 74 CTA pairs: the 12 tiles of the third round as 2 K partitions each
+    (1000, 10200, 1056),   # the same with ragged edges in M, N and K
+    (2304, 2816, 1024),    # 99 tiles in two raster groups: the 25 tail tiles span both
+    (512, 10240, 4096),    # 80 tiles: 6 tail tiles as 8 partitions each
+    (1024, 6144, 4096),    # 96 tiles: 22 as 3 partitions each
+])
+def test_large_shape_kernel_splits_a_short_last_round(qm, cuda_clean, oracle, m, n, k):
+    """gemm_tc2_kernel with more tiles than CTA pairs and a short last round: the tiles of that round run as K partitions that
+    add into tiles zeroed by zero_tail_tiles_kernel (TMA reduce-add).  Against the oracle, against the same kernel with whole
+    tiles only, twice in a row, and into a C that was full of garbage."""
+    from quadmul_b200 import _lib
+
+    torch = cuda_clean
+    p = qm.plan(m, n, k)
+    assert p["kernel"] == _lib.QM_KERNEL_TC and p["tile_n"] == 256 and p["stream_k"] == 2 and p["split_k"] == 1, p
+    ap = oracle.fill_packed(m, k, 771); bp = oracle.fill_packed(n, k, 772)
+    want = oracle.gemm(ap, bp)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    for _ in range(2):
+        c = torch.full((m, n), 0x5A5A5A5A, dtype=torch.int32, device="cuda")
+        qm.gemm(a, b, c, m, n, k)
+        torch.cuda.synchronize()
+        assert np.array_equal(c.cpu().numpy(), want), mismatch_report(c.cpu().numpy(), want)
+    whole = torch.full((m, n), -1, dtype=torch.int32, device="cuda")
+    qm.gemm_ex(a, b, whole, m, n, k, kernel=1, tile_n=256, swap_ab=1, cta_pair=2, a_tmem=2)  # explicit form: whole tiles only
+    assert torch.equal(whole, c)
+    assert qm.device_status() == (0, 0)
+
+
 @pytest.mark.parametrize("m,n,k,launches,opts", [
     (8192, 8192, 8192, 400, {}),                                              # large-shape kernel, 1024 tiles per launch
     (2048, 4096, 11008, 300, {}),
+    (1024, 10240, 2048, 400, {}),                                             # large-shape kernel, last round of tiles cut into K partitions
     (4096, 4096, 4096, 300, dict(kernel=1, tile_n=128, swap_ab=1, cta_pair=1)),  # single-CTA tile of the general kernel
     (16, 11008, 4096, 1500, {}),                                              # register-resident kernel, three rounds of blocks
     (16, 11008, 8448, 800, {}),                                               # decode kernel, two CTAs per SM
