@@ -573,6 +573,14 @@ def test_large_shape_kernel_splits_a_short_last_round(qm, cuda_clean, oracle, m,
     whole = torch.full((m, n), -1, dtype=torch.int32, device="cuda")
     qm.gemm_ex(a, b, whole, m, n, k, kernel=1, tile_n=256, swap_ab=1, cta_pair=2, a_tmem=2)  # explicit form: whole tiles only
     assert torch.equal(whole, c)
+    # as a column slab of a wider C (row pitch ldc): the zeroing must stay inside the slab
+    ldc, off = n + 512, 256
+    wide = torch.full((m, ldc), -5, dtype=torch.int32, device="cuda")
+    st = _lib.LIB.qm_gemm_s4_ldc(a.data_ptr(), b.data_ptr(), wide.data_ptr() + 4 * off, m, n, k, ldc, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert torch.equal(wide[:, off : off + n], c)
+    assert bool((wide[:, :off] == -5).all()) and bool((wide[:, off + n :] == -5).all())
     assert qm.device_status() == (0, 0)
 
 
