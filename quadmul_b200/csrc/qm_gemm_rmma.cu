@@ -106,20 +106,21 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         else return 4 * (t0 + u * kWarps) + q;
     };
 
-    // L2 prefetch of one block of weights (this lane's share): returns no data, touches nothing the program can observe
+    // L2 prefetch of one block of weights: returns no data, touches nothing the program can observe.  One bulk prefetch per row
+    // of the block (per 4 KB of a pre-laid-out block) instead of one instruction per 128-byte line keeps the load path free
+    // for the loads themselves.
     auto prefetch_block = [&](int rb) {
         if (rb >= num_blocks) return;
         if constexpr (PRE) {
-            // a warp's round is 32 * kMaxSteps * kRowGroups * 16 contiguous bytes: one 128-byte line per lane and 4 KB
-            for (int r = 0; r < rounds_k; ++r)
-                for (int b = 0; b < kMaxSteps * kRowGroups * 512; b += 4096)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(pre_base(rb, r) - lane) + b + lane * 128));
+            // a block is rounds_k x kWarps x (32 kMaxSteps kRowGroups 16) contiguous bytes
+            const int pieces = rounds_k * kWarps * (32 * kMaxSteps * kRowGroups * 16) / 4096;
+            const uint8_t *base = reinterpret_cast<const uint8_t *>(B) + (int64_t)rb * pieces * 4096;
+            for (int i = threadIdx.x; i < pieces; i += kThreads)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (int64_t)i * 4096), "r"(4096) : "memory");
         } else {
-            // every 128-byte line of the block exactly once: thread i takes line i % lines_per_row of row i / lines_per_row
-            const int lines_per_row = (int)((row_bytes + 127) / 128);
-            for (int i = threadIdx.x; i < kRowsPerCta * lines_per_row; i += kThreads) {
-                const int row = rb * kRowsPerCta + i / lines_per_row;
-                if (row < n) asm volatile("prefetch.global.L2 [%0];" ::"l"(B + (int64_t)row * row_bytes + (int64_t)(i % lines_per_row) * 128));
+            for (int i = threadIdx.x; i < kRowsPerCta; i += kThreads) {
+                const int row = rb * kRowsPerCta + i;
+                if (row < n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(B + (int64_t)row * row_bytes), "r"((int)row_bytes) : "memory");
             }
         }
     };
