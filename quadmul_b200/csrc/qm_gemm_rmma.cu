@@ -67,7 +67,12 @@ __device__ __forceinline__ uint32_t word(const uint4 &v, int s) { return s == 0 
 // of K) and lane (g, q) loads chunks 2q and 2q + 1 of its row in one instruction, so that the four lanes of a row read one
 // whole 128-byte line where MODE 0 / 2 read 64 bytes of it; the rows of A are indexed by the same chunks, so every product
 // still pairs equal K indices.
-template <int WARPS, int RG, int MS, int MODE>
+//
+// TOK8 (m <= 8): the operands of the MMA change places.  Two 8-row groups of B are the 16 rows of the instruction's first
+// operand (rows g and g + 8 of a lane come from the registers of group 2i and 2i + 1) and tokens 0..7 its eight columns, so a
+// round takes half as many mma.sync (the instruction costs the same for 8 tokens as for 16) and half as many partial sums go
+// through the reduction.
+template <int WARPS, int RG, int MS, int MODE, bool TOK8>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS == 16 ? 1 : 2))
 gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, int32_t *__restrict__ C, int64_t ldc, int m, int n, int k,
                  uint16_t *__restrict__ out_bf16, const float *__restrict__ scale_a, const float *__restrict__ scale_b)
@@ -77,6 +82,8 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                   kMaxSteps = Cfg::kMaxSteps;
     constexpr bool PRE = MODE == 1, WIDE = MODE == 3, FULL = MODE == 2 || WIDE;
     static_assert(!WIDE || MS == 2, "two chunks per 256-bit load");
+    static_assert(!TOK8 || RG % 2 == 0, "row groups are paired");
+    constexpr int kAcc = TOK8 ? kRowGroups / 2 : kRowGroups;  // accumulator tiles (m16n8) per warp
     extern __shared__ uint4 smem_u4[];
     // The rows of A stay PACKED in shared memory, [16 tiles rows][chunks + 4] 16-byte units (the 64 bytes of padding put the two
     // rows a quarter-warp reads at once on different banks); the A fragments are split when they are read.
@@ -175,7 +182,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         }
     };
     // d += (token tile tt of the packed rows of A in shared memory, split here) x (the weights of one round)
-    auto mma_round_packed = [&](int(&d)[kRowGroups][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0, int tt) {
+    auto mma_round_packed = [&](int(&d)[kAcc][4], const uint4(&w)[kMaxSteps][kRowGroups], int t0, int tt) {
 #pragma unroll
         for (int u = 0; u < kMaxSteps; ++u) {
             const int t = t0 + u * kWarps;
@@ -184,7 +191,22 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
                 uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
                 if (FULL || c < chunks) {
                     p0 = a_pk[(16 * tt + g) * pk_stride + c];
-                    p1 = a_pk[(16 * tt + g + 8) * pk_stride + c];
+                    if constexpr (!TOK8) p1 = a_pk[(16 * tt + g + 8) * pk_stride + c];
+                }
+                if constexpr (TOK8) {
+                    // second operand: token g, k = 4q..4q+3 from the even half and 16+4q.. from the odd half of the chunk
+                    uint4 tlo, thi;
+                    tc::split_s4x32(p0, tlo, thi);
+#pragma unroll
+                    for (int i = 0; i < kAcc; ++i) {
+                        uint4 wl0, wh0, wl1, wh1;
+                        tc::split_s4x32(w[u][2 * i], wl0, wh0);
+                        tc::split_s4x32(w[u][2 * i + 1], wl1, wh1);
+#pragma unroll
+                        for (int s = 0; s < 4; ++s)
+                            mma_s8(d[i], word(wl0, s), word(wl1, s), word(wh0, s), word(wh1, s), word(tlo, s), word(thi, s));
+                    }
+                    continue;
                 }
                 uint4 alo0, ahi0, alo1, ahi1;
                 tc::split_s4x32(p0, alo0, ahi0);
@@ -201,24 +223,45 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
         }
     };
     // partial tiles of all warps -> shared memory -> one output per thread (token tile tt, block rb); two barriers
-    auto reduce_store = [&](const int(&d)[kRowGroups][4], int rb, int tt) {
+    auto reduce_store = [&](const int(&d)[kAcc][4], int rb, int tt) {
+        int sum = 0, tok, col;
+        bool mine = true;
+        if constexpr (TOK8) {
+            // [warp][pair i][j][32]: register j of lane l at position (l + 2 i + (j >> 1)) % 32.  Lane (g, q) holds rows g (j = 0, 1)
+            // and g + 8 (j = 2, 3) of the 16 rows of pair i, tokens 2q (j even) and 2q + 1 (j odd).
 #pragma unroll
-        for (int rg = 0; rg < kRowGroups; ++rg)
+            for (int i = 0; i < kAcc; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) red[((warp * kRowGroups + rg) * 4 + j) * 32 + ((lane + 4 * (2 * rg + (j & 1))) & 31)] = d[rg][j];
-        __syncthreads();
-        const int tok = threadIdx.x / kRowsPerCta, col = threadIdx.x % kRowsPerCta;  // 16 tokens x kRowsPerCta rows of B
-        const int rg = col >> 3, cc = col & 7;
-        // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
-        const int src_lane = (tok & 7) * 4 + (cc >> 1);
-        const int j = (cc & 1) + (tok >= 8 ? 2 : 0);
-        int sum = 0;
+                for (int j = 0; j < 4; ++j) red[((warp * kAcc + i) * 4 + j) * 32 + ((lane + 2 * i + (j >> 1)) & 31)] = d[i][j];
+            __syncthreads();
+            // 8 tokens x kRowsPerCta rows of B: the first 8 kRowsPerCta threads take one output each
+            tok = threadIdx.x / kRowsPerCta, col = threadIdx.x % kRowsPerCta;
+            mine = tok < 8;
+            if (mine) {
+                const int rg = col >> 3, i = rg >> 1, half = rg & 1;
+                const int src_lane = (col & 7) * 4 + (tok >> 1);
+                const int j = 2 * half + (tok & 1);
 #pragma unroll
-        for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 4 + j) * 32 + ((src_lane + 4 * (2 * rg + (j & 1))) & 31)];
+                for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kAcc + i) * 4 + j) * 32 + ((src_lane + 2 * i + half) & 31)];
+            }
+        } else {
+#pragma unroll
+            for (int rg = 0; rg < kRowGroups; ++rg)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) red[((warp * kRowGroups + rg) * 4 + j) * 32 + ((lane + 4 * (2 * rg + (j & 1))) & 31)] = d[rg][j];
+            __syncthreads();
+            tok = threadIdx.x / kRowsPerCta, col = threadIdx.x % kRowsPerCta;  // 16 tokens x kRowsPerCta rows of B
+            const int rg = col >> 3, cc = col & 7;
+            // accumulator layout of m16n8: lane (g, q) holds (row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)
+            const int src_lane = (tok & 7) * 4 + (cc >> 1);
+            const int j = (cc & 1) + (tok >= 8 ? 2 : 0);
+#pragma unroll
+            for (int ww = 0; ww < kWarps; ++ww) sum += red[((ww * kRowGroups + rg) * 4 + j) * 32 + ((src_lane + 4 * (2 * rg + (j & 1))) & 31)];
+        }
         sum >>= 8;
         const int token = 16 * tt + tok;
         const int p = rb * kRowsPerCta + col;
-        if (token < m && p < n) {
+        if (mine && token < m && p < n) {
             if (out_bf16)
                 out_bf16[(int64_t)token * ldc + p] =
                     (uint16_t)dequant_bf16_bits(sum, scale_a ? __ldg(scale_a + token) : 1.0f, scale_b ? __ldg(scale_b + p) : 1.0f);
@@ -231,7 +274,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
     const bool resident = steps <= kWarps * kMaxSteps;     // a block's weights fit one round of registers (the host requires it for tiles > 1)
     bool a_ready = false;
     for (int rb = blockIdx.x; rb < num_blocks; rb += gridDim.x) {
-        int d[kRowGroups][4];
+        int d[kAcc][4];
         uint4 w[kMaxSteps][kRowGroups];
         if (resident) {
             // the weights stay in registers while the token tiles pass through shared memory one after the other
@@ -243,7 +286,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             }
             for (int tt = 0; tt < tiles; ++tt) {
 #pragma unroll
-                for (int rg = 0; rg < kRowGroups; ++rg)
+                for (int rg = 0; rg < kAcc; ++rg)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) d[rg][j] = 0;
                 mma_round_packed(d, w, warp, tt);
@@ -251,7 +294,7 @@ gemm_rmma_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, i
             }
         } else {
 #pragma unroll
-            for (int rg = 0; rg < kRowGroups; ++rg)
+            for (int rg = 0; rg < kAcc; ++rg)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) d[rg][j] = 0;
             for (int t0 = warp; t0 < steps; t0 += kWarps * kMaxSteps) {
@@ -302,11 +345,11 @@ __global__ void __launch_bounds__(256) prelayout_kernel(const uint8_t *__restric
     }
 }
 
-template <int WARPS, int RG, int MS, int MODE>
-static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
+template <int WARPS, int RG, int MS, int MODE, bool TOK8>
+static int rmma_launch_tok(const GemmArgs &g, const DeviceCtx &ctx)
 {
     using Cfg = RmmaCfg<WARPS, RG, MS>;
-    auto kernel = gemm_rmma_kernel<WARPS, RG, MS, MODE>;
+    auto kernel = gemm_rmma_kernel<WARPS, RG, MS, MODE, TOK8>;
     const int tiles = (g.m + 15) / 16;
     const size_t smem = (size_t)16 * tiles * (g.k / 2 + 64) + Cfg::kRedBytes;  // packed rows of A, padded by 64 bytes
     static std::atomic<bool> configured[64];  // set once per device; a repeated cudaFuncSetAttribute is harmless
@@ -337,6 +380,15 @@ static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
                                        g.scale_b);
     if (e != cudaSuccess) return record_cuda_error(e, "gemm_rmma_kernel launch");
     return QM_OK;
+}
+
+// up to eight rows of A take the form with the operands of the MMA exchanged
+template <int WARPS, int RG, int MS, int MODE>
+static int rmma_launch_cfg(const GemmArgs &g, const DeviceCtx &ctx)
+{
+    static const bool allow_tok8 = !std::getenv("QM_RMMA_NO_TOK8");
+    if (g.m <= 8 && allow_tok8) return rmma_launch_tok<WARPS, RG, MS, MODE, true>(g, ctx);
+    return rmma_launch_tok<WARPS, RG, MS, MODE, false>(g, ctx);
 }
 
 int rmma_launch(const GemmArgs &g, const DeviceCtx &ctx)

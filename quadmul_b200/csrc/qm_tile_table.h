@@ -42,8 +42,10 @@ inline double decode_cost(int family, int m, int n, int k, int num_sms)
     const double mb = (double)n * k / 2 / 1e6;
     if (family == kFamRmma) {
         const double rounds = (double)(((n + 31) / 32 + num_sms - 1) / num_sms), tiles = (double)((m + 15) / 16), kq = k / 4096.0;
+        const double half = m <= 8 ? 1.0 : 0.0;  // up to 8 rows of A: half as many MMAs per round
         const double *c = table::kRmmaCost;
-        return c[0] + c[1] * rounds + c[2] * kq + c[3] * rounds * kq + c[4] * tiles + c[5] * rounds * tiles;
+        return c[0] + c[1] * rounds + c[2] * kq + c[3] * rounds * kq + c[4] * tiles + c[5] * rounds * tiles + c[6] * half +
+               c[7] * rounds * kq * half;
     }
     if (family == kFamGemv) {
         const double *c = table::kGemvCost;
