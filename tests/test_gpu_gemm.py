@@ -593,7 +593,9 @@ def test_large_shape_kernel_splits_a_short_last_round(qm, cuda_clean, oracle, m,
     (16, 11008, 8448, 800, {}),                                               # decode kernel, two CTAs per SM
     (64, 4096, 4096, 1500, {}),                                               # register-resident kernel, four tiles of A
     (64, 4096, 8192, 800, {}),                                                # decode kernel, cluster reduction
-    (1, 11008, 4096, 1500, {}),                                               # dp4a row kernel
+    (1, 11008, 4096, 1500, {}),                                               # register-resident kernel, 8-token form, three rounds
+    (1, 11008, 4096, 1500, dict(kernel=3)),                                   # dp4a row kernel
+    (8, 4096, 4096, 1500, {}),                                                # register-resident kernel, 8-token form
     (16, 4096, 4096, 1500, {}),                                               # register-resident mma.sync kernel
     (16, 4096, 16384, 800, {}),                                               # decode kernel, K partitions through scratch
     # opt-in (QM_STRESS=1): long enough that a residual rate of 0.05 % per launch would show (about 15 s each)
