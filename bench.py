@@ -47,8 +47,8 @@ UNIT = "TOPS"
 INT8_PEAK_NOMINAL_TOPS = 4500.0  # NVIDIA's dense int8 figure for B200
 FALLBACK_BF16_TFLOPS = 1590.0    # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the headline kernel at 8192^3, from an ncu capture of this
-# command (`--steps 2 --warmup 3 --no-cpu-baseline --no-e2e --no-extra`, one launch captured): 164.3 MB read + 220.5 MB written
-DRAM_TRAFFIC_BYTES_PER_LAUNCH = 384.7e6
+# command (`--steps 2 --warmup 3 --no-cpu-baseline --no-e2e --no-extra`, one launch captured): 164.1 MB read + 221.0 MB written
+DRAM_TRAFFIC_BYTES_PER_LAUNCH = 385.1e6
 
 
 def config(n_gpus: int) -> dict:
