@@ -41,6 +41,33 @@ def test_shards_emulated_on_one_gpu(qm, cuda_clean, oracle, world, m, n, k):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("m,n,k,pitch,offset", [
+    (300, 1024, 512, 1024, 0),      # ragged rows, large-shape kernel
+    (1024, 2000, 1056, 2560, 256),  # ragged columns, a column slab of a wider C, K tail
+    (520, 1022, 256, 1030, 4),      # row pitch that is not a multiple of 4 elements: no 16-byte vector stores
+    (257, 513, 128, 513, 0),        # odd row pitch
+])
+def test_plain_store_epilogue_as_used_for_a_peer_destination(qm, cuda_clean, oracle, m, n, k, pitch, offset):
+    """plain_stores = 1 (what a rank passes when C lives in another GPU's memory): the large-shape kernel writes C with ordinary
+    stores (blocks transposed through shared memory into row segments) instead of TMA stores, here into local memory.  Ragged
+    edges, a slab of a wider C whose other columns must stay untouched, pitches that rule out vector stores."""
+    torch = cuda_clean
+    from quadmul_b200.sharded import NShardedGemm
+
+    ap = oracle.fill_packed(m, k, 31); bp = oracle.fill_packed(n, k, 32)
+    want = oracle.gemm(ap, bp)
+    a, b = to_dev(torch, ap), to_dev(torch, bp)
+    wide = torch.full((m, pitch), -5, dtype=torch.int32, device="cuda")
+    sh = NShardedGemm(n, world=1, rank=0)
+    for _ in range(2):
+        sh.local(a, b, m, k, out=wide[:, offset : offset + n], plain_stores=True)
+    torch.cuda.synchronize()
+    got = wide.cpu().numpy()
+    assert np.array_equal(got[:, offset : offset + n], want)
+    assert (got[:, :offset] == -5).all() and (got[:, offset + n :] == -5).all()
+    assert qm.device_status() == (0, 0)
+
+
 def test_call_on_a_device_that_is_not_current(qm, cuda_clean, oracle):
     """The reference launches on whichever device is current (extension.cpp:17-23 has no device guard); this mirror
     switches to the operands' device for the call."""
