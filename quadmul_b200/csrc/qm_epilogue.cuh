@@ -58,6 +58,45 @@ __device__ __forceinline__ void store_block_rows(const uint32_t (&v)[CH], uint32
     __syncwarp();  // the buffer is rewritten by the next block
 }
 
+// The same for a whole 32 x 32 block through a 4 KB buffer without padding: 16-byte piece j of row r sits at piece j ^ (r & 7)
+// (conflict-free both ways), and a warp-wide store writes four whole 128-byte row segments.  Full segments matter when C is
+// in another GPU's memory: they make better NVLink packets than the 64-byte pieces of two half blocks.
+__device__ __forceinline__ void store_block_rows_swizzled(const uint32_t (&v)[32], uint32_t stage, int lane, int32_t *__restrict__ C,
+                                                          int64_t ldc, int row0, int col0, int M, int N, bool vec_ok)
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4 o;
+        o.x = (uint32_t)((int32_t)v[4 * j] >> 8);
+        o.y = (uint32_t)((int32_t)v[4 * j + 1] >> 8);
+        o.z = (uint32_t)((int32_t)v[4 * j + 2] >> 8);
+        o.w = (uint32_t)((int32_t)v[4 * j + 3] >> 8);
+        ptx::sts128(stage + lane * 128 + (((uint32_t)j ^ ((uint32_t)lane & 7u)) << 4), o);
+    }
+    __syncwarp();
+    const int sub = lane >> 3, piece = lane & 7;
+    const int q = col0 + piece * 4;
+    int32_t *dst = C + (int64_t)(row0 + sub) * ldc + q;
+    // (not unrolled: this path is not the common one, and eight row pointers in flight would cost the kernel registers)
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i, dst += 4 * ldc) {
+        const int r = i * 4 + sub;
+        const uint4 o = ptx::lds128(stage + r * 128 + (((uint32_t)piece ^ ((uint32_t)r & 7u)) << 4));
+        const int row = row0 + r;
+        if (row < M) {
+            if (vec_ok && q + 3 < N) {
+                *reinterpret_cast<uint4 *>(dst) = o;
+            } else {
+                if (q < N) dst[0] = (int32_t)o.x;
+                if (q + 1 < N) dst[1] = (int32_t)o.y;
+                if (q + 2 < N) dst[2] = (int32_t)o.z;
+                if (q + 3 < N) dst[3] = (int32_t)o.w;
+            }
+        }
+    }
+    __syncwarp();  // the buffer is rewritten by the next block
+}
+
 // ---- TMA-store form ---------------------------------------------------------------------------
 // The warp writes its 32 x 32 int32 block into a 4 KB shared-memory buffer in the 128-byte-swizzled
 // layout of the C tensor map (16-byte piece j of row r at piece j ^ (r & 7): conflict-free), and one lane

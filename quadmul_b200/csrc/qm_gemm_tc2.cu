@@ -315,14 +315,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
                     store_block_tma(v, buf, lane, &tmapC, col, row0, false, reduce_add);
                     buf_used = true;
                 } else {
-                    uint32_t h0[16], h1[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        h0[j] = v[j];
-                        h1[j] = v[16 + j];
-                    }
-                    store_block_rows<16>(h0, buf, lane, C, ldc, row0, col, M, N, vec_ok);
-                    store_block_rows<16>(h1, buf, lane, C, ldc, row0, col + 16, M, N, vec_ok);
+                    store_block_rows_swizzled(v, buf, lane, C, ldc, row0, col, M, N, vec_ok);
                 }
             };
             uint32_t va[32], vb[32];
