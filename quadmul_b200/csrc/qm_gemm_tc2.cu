@@ -135,6 +135,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
     using Cfg = Tc2Cfg<H>;
     constexpr int S = Cfg::S, SP = Cfg::SP;
     extern __shared__ uint8_t smem_raw[];
+    // Programmatic dependent launch: the next kernel of the stream may begin its set-up now, and this kernel's own set-up
+    // (barriers, TMEM, tensor-map prefetch) runs while the previous kernel drains.  The TMA producer waits for the previous
+    // kernel before its first load; every other access to global memory follows data that the producer loaded.
+    grid_launch_dependents();
     const uint32_t raw_u32 = smem_u32(smem_raw);
     const uint32_t cv0 = (raw_u32 + 1023u) & ~1023u;   // converted B stages: [stage][sub-block][row][128 B]
     const uint32_t pk0 = cv0 + S * Cfg::kCvStage;      // packed stages: [stage][A sub-blocks (swizzle 64B)][B sub-blocks (linear)]
@@ -204,6 +208,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            grid_dependency_wait();  // nothing before this line read or wrote global memory
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tp, tq;
                 tile_coords(item_tile(t), tilesP, tilesQ, tp, tq);
@@ -485,6 +490,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant
 // those tiles add into them with TMA reduce-add.  C is 16-byte aligned with a row pitch of whole 16 bytes.
 __global__ void __launch_bounds__(256) zero_tail_tiles_kernel(int32_t *__restrict__ C, int64_t ldc, int M, int N, int tail_tiles)
 {
+    grid_launch_dependents();  // the GEMM that follows may set itself up meanwhile; it waits for this grid before its first load
+    grid_dependency_wait();    // the kernel before this one may still be writing the same C
     const int tilesP = (M + 255) / 256, tilesQ = (N + kBN - 1) / kBN;
     int tp, tq;
     tile_coords(tilesP * tilesQ - tail_tiles + (int)(blockIdx.x >> 3), tilesP, tilesQ, tp, tq);
@@ -528,8 +535,24 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k, boo
         st = make_c_tmap(&tmC, g.C, g.m, g.n, g.ldc);
         if (st != QM_OK) return st;
     }
+    static const bool allow_pdl = !std::getenv("QM_NO_PDL");
+    // zeroes the last `count` tiles of the static order
+    auto zero_tiles = [&](int count) -> int {
+        cudaLaunchConfig_t zc = {};
+        zc.gridDim = dim3((unsigned)(count * 8), 1, 1);
+        zc.blockDim = dim3(256, 1, 1);
+        zc.stream = g.stream;
+        cudaLaunchAttribute za[1];
+        za[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        za[0].val.programmaticStreamSerializationAllowed = 1;
+        zc.attrs = za;
+        zc.numAttrs = allow_pdl ? 1 : 0;
+        cudaError_t ze = cudaLaunchKernelEx(&zc, zero_tail_tiles_kernel, g.C, g.ldc, g.m, g.n, count);
+        return ze == cudaSuccess ? QM_OK : record_cuda_error(ze, "zero_tail_tiles_kernel launch");
+    };
     if (split_k > 1) {
-        // the K partitions accumulate with TMA reduce-add: needs the TMA path and a C that starts at zero
+        // the K partitions accumulate with TMA reduce-add: needs the TMA path and a C that starts at zero (a memset node is
+        // faster here than the zeroing kernel: 256 x 4096 x 4096 15.6 against 16.9 us)
         if (!use_tma_store) return QM_ERR_ALIGN;
         cudaError_t me = cudaMemset2DAsync(g.C, (size_t)g.ldc * 4, 0, (size_t)g.n * 4, (size_t)g.m, g.stream);
         if (me != cudaSuccess) return record_cuda_error(me, "cudaMemset2DAsync(C)");
@@ -539,13 +562,15 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k, boo
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Tc2Cfg<H>::kSmemBytes;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 1;  // the occupancy query below takes the cluster shape only
     // static tile list: every pair of the grid must be resident at once
     // per-device cache; the value is the same whichever thread computes it, so an atomic word is enough
     static std::atomic<int> max_pairs[64];
@@ -568,10 +593,10 @@ int tc2_launch_variant(const GemmArgs &g, const DeviceCtx &ctx, int split_k, boo
     // as 6 partitions each).
     int tail_tiles = 0, tail_split = 1;
     if (split_tail && !DQ && split_k == 1 && use_tma_store && tc2_tail_plan(tiles, units, num_kb, &tail_tiles, &tail_split)) {
-        zero_tail_tiles_kernel<<<(unsigned)(tail_tiles * 8), 256, 0, g.stream>>>(g.C, g.ldc, g.m, g.n, tail_tiles);
-        cudaError_t ze = cudaPeekAtLastError();
-        if (ze != cudaSuccess) return record_cuda_error(ze, "zero_tail_tiles_kernel launch");
+        st = zero_tiles(tail_tiles);
+        if (st != QM_OK) return st;
     }
+    cfg.numAttrs = allow_pdl ? 2 : 1;
     cfg.gridDim = dim3((unsigned)(units * 2), 1, 1);
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, use_tma_store, g.C, g.ldc, g.m, g.n, g.k, ctx.status, split_k, tail_tiles,
                                        tail_split, g.scale_a, g.scale_b);
