@@ -18,8 +18,12 @@
 // words of the same chunks, so every product pairs equal K indices.  The 16 partial 16 x 32 tiles of a CTA meet in shared
 // memory, are summed by 512 threads (one output each), shifted by 8 and stored as 128-byte row segments.
 //
+// With at most eight rows of A the operands of the MMA change places (TOK8 below): 16 rows of B x 8 tokens per instruction,
+// half as many instructions per round.
+//
 // Launches chain through programmatic dependent launch; before griddepcontrol.wait a CTA only prefetches its weights into
-// L2 (no data is returned, so this is correct whatever the previous kernel writes).
+// L2 (no data is returned, so this is correct whatever the previous kernel writes).  Prefetches are bulk prefetches, one per
+// row of a block, so that they do not compete with the loads for the load path.
 #include <atomic>
 #include <cstdlib>
 
