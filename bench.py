@@ -465,6 +465,12 @@ def multi_gpu_legs(torch, dist, qm, world: int, rank: int, steps: int = 2) -> di
         sh.gather(c_local, m, out=full_c)
 
     nccl_ms = timed(with_nccl, steps)
+
+    def with_nccl_to_rank0():
+        sh.local(a, b, m, k, out=c_local)
+        sh.gather_to(c_local, m, dst=0, out=full_c if rank == 0 else None)
+
+    nccl_to0_ms = timed(with_nccl_to_rank0, steps)
     del full_c
     torch.cuda.empty_cache()
     csym = SymmetricC(m, n)
@@ -499,8 +505,9 @@ def multi_gpu_legs(torch, dist, qm, world: int, rank: int, steps: int = 2) -> di
     ops = 2.0 * m * n * k
     result["large"] = {"shape": [m, n, k], "world": world, "scaling": "strong", "steps": steps,
                        "compute_ms": compute_ms, "compute_tops": ops / (compute_ms * 1e-3) / 1e12,
-                       "nccl_gather_ms": nccl_ms, "fused_gather_ms": fused_ms,
-                       "note": "B column-sharded, A replicated; *_gather_ms = GEMM + bringing the full int32 C to rank 0 (NCCL: to every rank); "
+                       "nccl_gather_ms": nccl_ms, "nccl_gather_to_rank0_ms": nccl_to0_ms, "fused_gather_ms": fused_ms,
+                       "note": "B column-sharded, A replicated; *_gather_ms = GEMM + bringing the full int32 C together (nccl_gather: all-gather, to "
+                               "every rank; nccl_gather_to_rank0: NCCL gather, to rank 0 only; fused: to rank 0 only); "
                                "fused: GEMM epilogues store into rank 0's C over NVLink, completion flags with a bounded wait; "
                                "rank 0's gathered C sampled against the CPU oracle"}
     del csym, a, b, c_local

@@ -83,6 +83,34 @@ class NShardedGemm:
         check(st, f"sharded gemm rank {self.rank}")
         qm._launches += 1
 
+    def gather_to(self, slab, m: int, dst: int = 0, out=None):
+        """Full row-major C[m, n] on rank `dst` only (NCCL gather = grouped send / receive, then the un-interleave kernel on
+        `dst`); returns None on the other ranks.  The library-collective counterpart of `local_into`."""
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return self.gather(slab, m, out=out)
+        if slab.shape[1] != self.slab_stride:
+            padded = torch.zeros((m, self.slab_stride), dtype=slab.dtype, device=slab.device)
+            padded[:, : self.count] = slab[:, : self.count]
+            slab = padded
+        slab = slab.contiguous()
+        if self.rank != dst:
+            dist.gather(slab, gather_list=None, dst=dst, group=self.group)
+            return None
+        slabs = torch.empty((self.world, m, self.slab_stride), dtype=slab.dtype, device=slab.device)
+        dist.gather(slab, gather_list=[slabs[r] for r in range(self.world)], dst=dst, group=self.group)
+        if out is None:
+            out = torch.empty((m, self.n), dtype=slab.dtype, device=slab.device)
+        if self._unshard_fn is not None:
+            self._unshard_fn(slabs, out, m, self.n, self.world, self.slab_stride)
+        else:
+            from . import unshard_c
+
+            unshard_c(slabs, out, m, self.n, self.world, self.slab_stride)
+        return out
+
     # -- fused gather: the GEMM epilogue writes straight into the destination rank's C ------------
     def local_into(self, a, b_shard, m: int, k: int, c_sym: "SymmetricC", dst: int = 0):
         """Compute this rank's column slab and store it, from inside the GEMM kernel, into rank `dst`'s

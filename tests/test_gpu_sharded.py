@@ -164,6 +164,9 @@ def _nccl_worker(rank, world, port, m, n, k, q):
         torch.cuda.synchronize()
         want = o.gemm(ap, bp)
         ok = bool(np.array_equal(full.cpu().numpy(), want))
+        only = sh.gather_to(slab, m, dst=0)  # NCCL gather to rank 0 alone
+        torch.cuda.synchronize()
+        ok = ok and ((only is None) if rank != 0 else bool(np.array_equal(only.cpu().numpy(), want)))
         # fused gather: every rank's GEMM epilogue stores its slab into rank 0's C over NVLink
         from quadmul_b200.sharded import SymmetricC
 

@@ -55,6 +55,10 @@ def _worker(rank, world, port, m, n, k, q):
         full = sh.gather(slab, m)
         want = o.gemm(ap, bp)
         ok = bool(np.array_equal(full.numpy(), want)) and bool(np.array_equal(slab.numpy(), want[:, sh.begin : sh.begin + sh.count]))
+        # the gather to one rank only: the last rank gets the full C, the others nothing
+        dst = world - 1
+        only = sh.gather_to(slab, m, dst=dst)
+        ok = ok and ((only is None) if rank != dst else bool(np.array_equal(only.numpy(), want)))
         q.put((rank, ok, sh.begin, sh.count))
     finally:
         dist.destroy_process_group()
